@@ -1,0 +1,139 @@
+// Registration of the library with PyTorch: two custom classes and the free
+// operators, under the reference's namespaces (reference: src/pybind.cpp:114-150).
+// Every method is registered under the upstream CUDA name and under the name
+// used by the MUSA checkout of the reference, so that scripts written against
+// either run unchanged.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/custom_class.h>
+#include <torch/library.h>
+
+#include "../kernels/rmsnorm.h"
+#include "baseline_impl.h"
+#include "checks.h"
+#include "overlap_impl.h"
+
+namespace fo {
+
+static std::vector<int64_t> generate_id_op() { return generate_nccl_id(); }
+
+// reorder_rmsnorm(X, RX, RW, BM, BN, rldn, RA): X holds a [bs, dim] matrix in
+// the tile-reordered layout, RX receives the RMS-normalised rows in natural
+// order (reference: src/rmsnorm/rmsnorm.cpp:10-23, eps fixed to 1e-5 there).
+static void reorder_rmsnorm_eps(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int64_t BN, int64_t rldn,
+                                at::Tensor RA, double eps) {
+  check_matrix(X, "X");
+  check_matrix(RX, "RX");
+  const DType dt = dtype_of(X);
+  TORCH_CHECK(RX.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(), "dtype mismatch");
+  TORCH_CHECK(RX.sizes() == X.sizes(), "RX must have the shape of X");
+  const int64_t bs = X.size(0), dim = X.size(1);
+  TORCH_CHECK(RW.is_cuda() && RW.is_contiguous() && RW.numel() == dim, "RW must hold dim values");
+  TORCH_CHECK(BM > 0 && BN > 0 && bs % BM == 0 && dim % BN == 0 && BN % 8 == 0 && dim % 8 == 0,
+              "need bs % BM == 0, dim % BN == 0, BN % 8 == 0");
+  check_int_tensor(RA, "RA", true);
+  const int64_t tiles = (bs / BM) * (dim / BN);
+  TORCH_CHECK(RA.numel() == tiles, "RA must have ", tiles, " entries, got ", RA.numel());
+  TORCH_CHECK(rldn >= 1 && tiles % rldn == 0, "rldn must divide the number of tiles");
+  OutLayout L{};
+  L.tiled = 1;
+  L.bm = static_cast<int>(BM);
+  L.bn = static_cast<int>(BN);
+  L.tn = static_cast<int>(dim / BN);
+  L.rldn = static_cast<int>(rldn);
+  L.ra = RA.data_ptr<int>();
+  L.ld = dim;
+  c10::cuda::CUDAGuard guard(X.device());
+  cudaError_t e = launch_reorder_rmsnorm(X.data_ptr(), RX.data_ptr(), RW.data_ptr(), static_cast<int>(bs),
+                                         static_cast<int>(dim), static_cast<float>(eps), L, dt,
+                                         at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "reorder_rmsnorm launch failed: ", cudaGetErrorString(e));
+}
+
+static void reorder_rmsnorm_op(at::Tensor X, at::Tensor RX, at::Tensor RW, int64_t BM, int64_t BN, int64_t rldn,
+                               at::Tensor RA) {
+  reorder_rmsnorm_eps(X, RX, RW, BM, BN, rldn, RA, 1e-5);
+}
+
+// rmsnorm(X, O, RW, eps): exists in the reference's C++ (src/rmsnorm/rmsnorm.cpp:25-36)
+// without being registered; registered here.
+static void rmsnorm_op(at::Tensor X, at::Tensor O, at::Tensor RW, double eps) {
+  check_matrix(X, "X");
+  check_matrix(O, "O");
+  const DType dt = dtype_of(X);
+  TORCH_CHECK(O.scalar_type() == X.scalar_type() && RW.scalar_type() == X.scalar_type(), "dtype mismatch");
+  TORCH_CHECK(O.sizes() == X.sizes(), "O must have the shape of X");
+  TORCH_CHECK(RW.is_cuda() && RW.is_contiguous() && RW.numel() == X.size(1), "RW must hold dim values");
+  TORCH_CHECK(X.size(1) % 8 == 0, "dim must be a multiple of 8");
+  c10::cuda::CUDAGuard guard(X.device());
+  cudaError_t e = launch_rmsnorm(X.data_ptr(), O.data_ptr(), RW.data_ptr(), static_cast<int>(X.size(0)),
+                                 static_cast<int>(X.size(1)), static_cast<float>(eps), dt,
+                                 at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(e == cudaSuccess, "rmsnorm launch failed: ", cudaGetErrorString(e));
+}
+
+}  // namespace fo
+
+TORCH_LIBRARY(flashoverlap_class, m) {
+  using fo::BaselineImpl;
+  using fo::OverlapImpl;
+  m.class_<BaselineImpl>("BaselineImpl")
+      .def(torch::init<>())
+      .def("nccl_init", &BaselineImpl::NcclInit)
+      .def("mccl_init", &BaselineImpl::NcclInit)
+      .def("cublas_init", &BaselineImpl::CublasInit)
+      .def("mublas_init", &BaselineImpl::CublasInit)
+      .def("gemm_allreduce", &BaselineImpl::GemmAllReduce)
+      .def("gemm_reducescatter", &BaselineImpl::GemmReduceScatter)
+      .def("gemm_all2all", &BaselineImpl::GemmAll2All)
+      .def("cublas_gemm", &BaselineImpl::Gemm)
+      .def("mublas_gemm", &BaselineImpl::Gemm)
+      .def("nccl_allreduce", &BaselineImpl::NcclAllReduce)
+      .def("mccl_allreduce", &BaselineImpl::NcclAllReduce)
+      .def("nccl_reducescatter", &BaselineImpl::NcclReduceScatter)
+      .def("mccl_reducescatter", &BaselineImpl::NcclReduceScatter)
+      .def("nccl_all2all", &BaselineImpl::NcclAll2All)
+      .def("mccl_all2all", &BaselineImpl::NcclAll2All);
+
+  m.class_<OverlapImpl>("OverlapImpl")
+      .def(torch::init<>())
+      .def("nccl_init", &OverlapImpl::NcclInit)
+      .def("mccl_init", &OverlapImpl::NcclInit)
+      .def("cutlass_init", &OverlapImpl::CutlassInit)
+      .def("mutlass_init", &OverlapImpl::CutlassInit)
+      .def("overlap_init", &OverlapImpl::OverlapInit)
+      .def("cutlass_gemm", &OverlapImpl::Gemm)
+      .def("mutlass_gemm", &OverlapImpl::Gemm)
+      .def("gemm_allreduce_overlap", &OverlapImpl::GemmAllReduceOverlap)
+      .def("gemm_reducescatter_overlap", &OverlapImpl::GemmReduceScatterOverlap)
+      .def("gemm_allreduce", &OverlapImpl::GemmAllReduce)
+      .def("gemm_reducescatter", &OverlapImpl::GemmReduceScatter)
+      .def("gemm_all2all", &OverlapImpl::GemmAll2All)
+      .def("nccl_allreduce", &OverlapImpl::NcclAllReduce)
+      .def("mccl_allreduce", &OverlapImpl::NcclAllReduce)
+      .def("nccl_reducescatter", &OverlapImpl::NcclReduceScatter)
+      .def("mccl_reducescatter", &OverlapImpl::NcclReduceScatter)
+      .def("nccl_all2all", &OverlapImpl::NcclAll2All)
+      .def("mccl_all2all", &OverlapImpl::NcclAll2All)
+      .def("seg_allreduce", &OverlapImpl::SegAllReduce)
+      .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
+      .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
+      .def("gemm_rmsnorm", &OverlapImpl::GemmRmsNorm)
+      .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
+      .def("set_sm_count", &OverlapImpl::SetSmCount)
+      .def("set_raster_group", &OverlapImpl::SetRasterGroup)
+      .def("status", &OverlapImpl::Status)
+      .def("status_string", &OverlapImpl::StatusString)
+      .def("check_status", &OverlapImpl::CheckStatus)
+      .def("reset", &OverlapImpl::Reset)
+      .def("num_algos", &OverlapImpl::NumAlgos)
+      .def("algo_tile", &OverlapImpl::AlgoTile);
+}
+
+TORCH_LIBRARY(flashoverlap_op, m) {
+  m.def("generate_nccl_id", &fo::generate_id_op);
+  m.def("generate_mccl_id", &fo::generate_id_op);
+  m.def("reorder_rmsnorm", &fo::reorder_rmsnorm_op);
+  m.def("reorder_rmsnorm_eps", &fo::reorder_rmsnorm_eps);
+  m.def("rmsnorm", &fo::rmsnorm_op);
+}

@@ -1,0 +1,78 @@
+// torch.classes.flashoverlap_class.OverlapImpl: the public class of the
+// library.  Method names and argument lists follow the reference
+// (reference: src/overlap_impl.h:9-40, src/pybind.cpp:129-144); both the
+// upstream CUDA names (nccl_* / cutlass_*) and the names of the MUSA checkout
+// (mccl_* / mutlass_*) are registered.  The overlapped operations run as one
+// fused sm_100a kernel (FusedEngine); the non-overlapped ones run the same
+// GEMM kernel followed by an NCCL collective on the same stream.
+#pragma once
+
+#include <torch/custom_class.h>
+#include <torch/torch.h>
+
+#include <memory>
+
+#include "../runtime/engine.h"
+#include "nccl_utils.h"
+
+namespace fo {
+
+class OverlapImpl : public torch::CustomClassHolder {
+ public:
+  OverlapImpl();
+  ~OverlapImpl() override;
+
+  // ---- reference API ------------------------------------------------------
+  void NcclInit(int64_t rank, int64_t size, std::vector<int64_t> id);
+  void CutlassInit();
+  void OverlapInit();
+  void Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t algo);
+  void GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA, int64_t rLDN,
+                            at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo, bool if_monitor);
+  void GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, at::Tensor MM, at::Tensor RA,
+                                at::Tensor RE, int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo,
+                                bool if_monitor);
+  void GemmAllReduce(at::Tensor A, at::Tensor B, at::Tensor C, int64_t algo);
+  void GemmReduceScatter(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t algo);
+  void GemmAll2All(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, int64_t algo, at::Tensor mLen_CPU);
+  void NcclAllReduce(at::Tensor C);
+  void NcclReduceScatter(at::Tensor C);
+  void NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU);
+  void SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum);
+
+  // ---- fused entry points with natural-order results ----------------------
+  // GEMM + all-reduce (+ RMSNorm when `weight` is given).  Returns a tensor
+  // that aliases the symmetric result buffer (valid until the second next
+  // fused call on this object).
+  at::Tensor GemmAllReduceFused(at::Tensor A, at::Tensor B, c10::optional<at::Tensor> weight, double eps,
+                                int64_t algo);
+  // GEMM + reduce-scatter (+ RMSNorm) into D [M/size, N].
+  void GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, c10::optional<at::Tensor> weight, double eps,
+                              int64_t algo, bool interleave);
+  // GEMM + RMSNorm on one GPU: C receives A*B^T, O the normalised rows.
+  void GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
+                   int64_t algo);
+
+  // ---- tuning knobs and failure reporting ---------------------------------
+  void SetTimeoutMs(int64_t ms);
+  void SetSmCount(int64_t n);
+  void SetRasterGroup(int64_t g);
+  // [code, rank, where, seen, want]; code 0 = no failure reported.
+  std::vector<int64_t> Status();
+  std::string StatusString();
+  // Raises if a kernel reported a failure.
+  void CheckStatus();
+  void Reset();
+  int64_t NumAlgos();
+  std::vector<int64_t> AlgoTile(int64_t algo);
+
+ private:
+  GemmOperands operands(const at::Tensor& A, const at::Tensor& B, int64_t algo) const;
+  void require_comm(const char* op) const;
+
+  Communicator comm_;
+  FusedEngine engine_;
+  bool engine_ready_ = false;
+};
+
+}  // namespace fo

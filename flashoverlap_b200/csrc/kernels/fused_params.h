@@ -1,0 +1,108 @@
+// Parameter block of the persistent sm_100a GEMM(+collective)(+RMSNorm) kernel.
+//
+// One kernel covers what the reference spreads over a signalling GEMM, a
+// counting kernel and a series of NCCL calls (reference: src/overlap_impl.cu:221-328,
+// src/overlap/gemm_with_signal.h:127-202, src/overlap/gemm_with_scatter.h:127-197,
+// src/wait.cuh:5-9).  The GEMM phase writes every finished 32-row slab of an
+// output tile where its consumer needs it (own memory or a peer's staging
+// buffer) and bumps a counter on the owning GPU; the reduce phase, run by the
+// same CTAs once they are out of tiles, waits (bounded) on those counters, sums
+// the per-rank partials in fp32, optionally applies RMSNorm and writes the
+// result locally (reduce-scatter) or to every peer (all-reduce).
+#pragma once
+
+#include <cuda.h>
+#include <stdint.h>
+
+namespace fo {
+
+constexpr int kMaxRanks = 8;
+
+// Where an element (row, col) of a logical row-major matrix lives in memory.
+// tiled == 0: natural layout, offset = row * ld + col.
+// tiled == 1: the reference's "reordered" layout (reference:
+//   src/rmsnorm/rmsnorm.cuh:62-115, src/overlap/gemm_with_signal.h:148-165):
+//   the matrix is cut into bm x bn tiles, tile t = (row/bm)*tn + col/bn lives in
+//   slot s = ra[t]; with w = rldn*bn the element sits at
+//   ((s / rldn) * bm + row % bm) * w + (s % rldn) * bn + col % bn.
+struct OutLayout {
+  int tiled;
+  int bm, bn, tn, rldn;
+  const int* ra;
+  long long ld;
+};
+
+enum OwnMode : int {
+  OWN_SINGLE = 0,      // everything stays on this GPU (plain GEMM, TP = 1)
+  OWN_BLOCK = 1,       // owner(row) = row / rows_per_owner (contiguous reduce-scatter)
+  OWN_INTERLEAVE = 2,  // owner(row) = row % ws (all-reduce; reference-style reduce-scatter)
+};
+
+enum StatusCode : uint32_t {
+  ST_OK = 0,
+  ST_TIMEOUT_PIPE = 1,    // an mbarrier inside the GEMM pipeline never completed
+  ST_TIMEOUT_FLAG = 2,    // partials from some rank never arrived
+  ST_TIMEOUT_DONE = 3,    // all-reduce results from some owner never arrived
+  ST_BAD_INDEX = 4,       // an index array (reorder / row map) held an out-of-range entry
+  ST_TIMEOUT_GATHER = 5,  // an all-gathered operand shard never arrived
+};
+
+// Written by the device on the first error only; lives in mapped host memory.
+struct StatusWord {
+  uint32_t code;
+  uint32_t rank;
+  uint32_t where;  // role / unit that gave up
+  uint32_t seen;   // counter value seen
+  uint32_t want;   // counter value wanted
+  uint32_t pad[3];
+};
+
+struct alignas(64) FusedParams {
+  CUtensorMap tmA;  // A [M, K] row-major, box 64 x 128, 128-byte swizzle
+  CUtensorMap tmB;  // B [N, K] row-major, box 64 x BN,  128-byte swizzle
+
+  int M, N, K;
+  int TM, TN;        // tile grid (BM = 128)
+  int raster_group;  // tile rows walked column-major together (L2 reuse of B)
+  int rot;           // first tile row (rotates ranks apart in block-ownership mode)
+
+  // ---- GEMM epilogue destination -------------------------------------------
+  int own_mode;             // OwnMode
+  int ws, me;               // ranks in the group, this rank
+  int rows_per_owner;       // M / ws
+  void* epi_base[kMaxRanks];  // own_mode SINGLE: [0] = C; else staging slot of `me` on each owner
+  OutLayout epi_layout;       // layout within the destination (tiled only with OWN_SINGLE)
+  uint32_t* flag[kMaxRanks];  // per-owner arrival counters, one per tile row; null = no signalling
+
+  // ---- reference-compatible signalling / tracing ----------------------------
+  int* seg_counter;     // MM: per-segment tile counters (null = off)
+  const int* cseg;      // device copy of tiles-per-segment
+  int nseg;
+  int* ticket_counter;  // monitor mode: global completion ticket (null = off)
+  int* trace;           // monitor mode: trace[slot] = ticket
+  const int* slot_of_tile;  // RA; null = identity
+
+  // ---- A operand readiness (all-gather -> GEMM) -----------------------------
+  const uint32_t* a_ready;  // per source-rank counter; null = A is ready at launch
+  uint32_t a_ready_target;
+  int a_rows_per_rank;      // rows of A contributed by each rank
+
+  // ---- reduce phase ---------------------------------------------------------
+  int reduce;                      // 0 = kernel ends after the GEMM
+  const void* stage;               // this GPU's staging: [ws][rows_per_owner][N]
+  uint32_t flag_target;            // value every arrival counter must reach
+  int norm;                        // apply RMSNorm after the sum
+  const void* gamma;               // [N]
+  float eps;
+  int bcast;                       // 1 = write to every rank (all-reduce), 0 = only locally
+  void* out[kMaxRanks];            // destination of reduced rows on each rank
+  OutLayout out_layout;
+  uint32_t* done[kMaxRanks];       // per-rank "rows delivered" counter (all-reduce)
+  uint32_t done_target;
+
+  // ---- failure reporting ----------------------------------------------------
+  StatusWord* status;
+  unsigned long long timeout_ns;
+};
+
+}  // namespace fo

@@ -1,0 +1,278 @@
+#include "engine.h"
+
+#include <sstream>
+#include <stdexcept>
+
+namespace fo {
+
+namespace {
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(cuda_error_string(e, what));
+}
+void check_launch(cudaError_t e, const char* why, const char* op) {
+  if (e != cudaSuccess) {
+    std::string msg = std::string(op) + ": " + (why && *why ? why : "launch failed");
+    throw std::runtime_error(cuda_error_string(e, msg.c_str()));
+  }
+}
+constexpr size_t kFlagWords = FusedEngine::kMaxTileRows + 64;
+}  // namespace
+
+FusedEngine::~FusedEngine() {
+  if (status_dev_ != nullptr) cudaFree(status_dev_);
+  status_dev_ = nullptr;
+}
+
+void FusedEngine::init(int rank, int world, AllGatherFn all_gather) {
+  if (world < 1 || world > kMaxRanks) throw std::runtime_error("FusedEngine: world size must be 1..8");
+  if (rank < 0 || rank >= world) throw std::runtime_error("FusedEngine: bad rank");
+  rank_ = rank;
+  world_ = world;
+  all_gather_ = std::move(all_gather);
+  if (status_dev_ == nullptr) {
+    check(cudaMalloc(reinterpret_cast<void**>(&status_dev_), sizeof(StatusWord)), "cudaMalloc(status)");
+    check(cudaMemset(status_dev_, 0, sizeof(StatusWord)), "cudaMemset(status)");
+  }
+}
+
+uint32_t* FusedEngine::flag_ptr(int rank, int set) const {
+  return static_cast<uint32_t*>(heap_.ptr(rank, ws_.flags[set]));
+}
+uint32_t* FusedEngine::done_ptr(int rank, int set) const { return flag_ptr(rank, set) + kMaxTileRows; }
+
+void FusedEngine::ensure_workspace(long long m, long long n) {
+  const long long elems = m * n;
+  if (heap_.valid() && ws_.capacity_elems >= elems) return;
+  if (heap_.valid()) {
+    // Growing: all ranks get here in the same call.  Drain the device, then a
+    // gather as a barrier so that no peer still writes into the old slab.
+    check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    if (world_ > 1) {
+      char t = 1;
+      std::vector<char> all(world_);
+      all_gather_(&t, 1, all.data());
+    }
+    heap_.destroy();
+  }
+  const size_t mat = static_cast<size_t>(elems) * 2;
+  const size_t total = 4 * (mat + 4096) + 2 * (kFlagWords * 4 + 4096) + (1 << 20);
+  heap_.init(rank_, world_, total, all_gather_);
+  for (int s = 0; s < 2; ++s) ws_.stage[s] = heap_.alloc(mat, 1024);
+  for (int s = 0; s < 2; ++s) ws_.result[s] = heap_.alloc(mat, 1024);
+  for (int s = 0; s < 2; ++s) ws_.flags[s] = heap_.alloc(kFlagWords * 4, 1024);
+  ws_.capacity_elems = elems;
+  calls_ = 0;
+}
+
+void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
+  p = FusedParams{};
+  if (sig != nullptr) {
+    p.seg_counter = sig->seg_counter;
+    p.cseg = sig->cseg;
+    p.nseg = sig->nseg;
+    p.ticket_counter = sig->ticket_counter;
+    p.trace = sig->trace;
+    p.slot_of_tile = sig->slot_of_tile;
+  }
+  p.ws = world_;
+  p.me = rank_;
+  p.status = status_dev_;
+  p.timeout_ns = timeout_ns_;
+  p.raster_group = raster_group_;
+  p.epi_layout.ld = 0;
+}
+
+void FusedEngine::gemm(const GemmOperands& g_in, void* C, const OutLayout* layout, const SignalArgs* sig,
+                       cudaStream_t stream) {
+  if (!initialized()) init(0, 1, nullptr);
+  FusedParams p;
+  base_params(p, sig);
+  GemmOperands g = g_in;
+  if (g.sm_count == 0) g.sm_count = sm_count_;
+  p.own_mode = OWN_SINGLE;
+  p.ws = 1;
+  p.me = 0;
+  p.rows_per_owner = g.M;
+  p.epi_base[0] = C;
+  if (layout != nullptr) p.epi_layout = *layout;
+  else p.epi_layout.ld = g.N;
+  if (p.raster_group == 0) p.raster_group = 8;
+  const char* why = nullptr;
+  check_launch(launch_fused(g, p, stream, &why), why, "gemm");
+}
+
+void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* out, const NormArgs& norm,
+                               cudaStream_t stream) {
+  if (!initialized()) init(0, 1, nullptr);
+  ensure_workspace(1, 1);  // only the counters are needed
+  GemmOperands g = g_in;
+  if (g.sm_count == 0) g.sm_count = sm_count_;
+  const TileConfig tc = algo_config(g.algo);
+  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_rmsnorm: too many tile rows");
+  const int set = static_cast<int>(calls_ & 1ull);
+  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  FusedParams p;
+  base_params(p, nullptr);
+  p.own_mode = OWN_SINGLE;
+  p.ws = 1;
+  p.me = 0;
+  p.rows_per_owner = g.M;
+  p.epi_base[0] = scratch;
+  p.epi_layout.ld = g.N;
+  p.flag[0] = flag_ptr(rank_, set);
+  if (p.raster_group == 0) p.raster_group = 4;
+  p.reduce = 1;
+  p.stage = scratch;
+  p.flag_target = static_cast<uint32_t>((g.N / tc.bn) * 4);
+  p.norm = norm.gamma != nullptr;
+  p.gamma = norm.gamma;
+  p.eps = norm.eps;
+  p.bcast = 0;
+  p.out[0] = out;
+  p.out_layout.ld = g.N;
+  const char* why = nullptr;
+  check_launch(launch_fused(g, p, stream, &why), why, "gemm_rmsnorm");
+  ++calls_;
+}
+
+void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, const NormArgs& norm,
+                                  const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("gemm_allreduce: engine not initialised");
+  GemmOperands g = g_in;
+  if (g.sm_count == 0) g.sm_count = sm_count_;
+  const TileConfig tc = algo_config(g.algo);
+  if (g.M % world_ != 0) throw std::runtime_error("gemm_allreduce: M must be divisible by the world size");
+  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_allreduce: too many tile rows");
+  ensure_workspace(g.M, g.N);
+  const int set = static_cast<int>(calls_ & 1ull);
+  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+
+  FusedParams p;
+  base_params(p, sig);
+  const int rows_local = g.M / world_;
+  p.own_mode = world_ == 1 ? OWN_SINGLE : OWN_INTERLEAVE;
+  p.rows_per_owner = rows_local;
+  const size_t slot_bytes = static_cast<size_t>(rows_local) * g.N * 2;
+  for (int r = 0; r < world_; ++r) {
+    // my slot inside owner r's staging buffer
+    p.epi_base[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + slot_bytes * rank_;
+    p.flag[r] = flag_ptr(r, set);
+    p.out[r] = heap_.ptr(r, ws_.result[set]);
+    p.done[r] = done_ptr(r, set);
+  }
+  p.epi_layout.ld = g.N;
+  if (p.raster_group == 0) p.raster_group = 2;
+  p.reduce = 1;
+  p.stage = heap_.local(ws_.stage[set]);
+  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn) * 4);
+  p.norm = norm.gamma != nullptr;
+  p.gamma = norm.gamma;
+  p.eps = norm.eps;
+  p.bcast = 1;
+  if (out_layout != nullptr) p.out_layout = *out_layout;
+  else p.out_layout.ld = g.N;
+  p.done_target = static_cast<uint32_t>(g.M);
+  const char* why = nullptr;
+  check_launch(launch_fused(g, p, stream, &why), why, "gemm_allreduce");
+  ++calls_;
+  void* result = heap_.local(ws_.result[set]);
+  if (out_user != nullptr) {
+    check(cudaMemcpyAsync(out_user, result, static_cast<size_t>(g.M) * g.N * 2, cudaMemcpyDeviceToDevice, stream),
+          "cudaMemcpyAsync(result)");
+  }
+  return result;
+}
+
+void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool interleave, const NormArgs& norm,
+                                     const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("gemm_reducescatter: engine not initialised");
+  GemmOperands g = g_in;
+  if (g.sm_count == 0) g.sm_count = sm_count_;
+  const TileConfig tc = algo_config(g.algo);
+  if (g.M % world_ != 0) throw std::runtime_error("gemm_reducescatter: M must be divisible by the world size");
+  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_reducescatter: too many tile rows");
+  const int rows_local = g.M / world_;
+  if (!interleave && world_ > 1 && rows_local % tc.bm != 0) {
+    throw std::runtime_error("gemm_reducescatter: contiguous ownership needs (M / world) % 128 == 0");
+  }
+  ensure_workspace(g.M, g.N);
+  const int set = static_cast<int>(calls_ & 1ull);
+  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+
+  FusedParams p;
+  base_params(p, sig);
+  p.own_mode = world_ == 1 ? OWN_SINGLE : (interleave ? OWN_INTERLEAVE : OWN_BLOCK);
+  p.rows_per_owner = rows_local;
+  const size_t slot_bytes = static_cast<size_t>(rows_local) * g.N * 2;
+  for (int r = 0; r < world_; ++r) {
+    p.epi_base[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + slot_bytes * rank_;
+    p.flag[r] = flag_ptr(r, set);
+  }
+  p.epi_layout.ld = g.N;
+  if (p.own_mode == OWN_BLOCK) {
+    // start with the tile rows of the next rank so that at any moment the
+    // ranks push to different owners
+    p.rot = ((rank_ + 1) % world_) * (rows_local / tc.bm);
+  }
+  if (p.raster_group == 0) p.raster_group = 2;
+  p.reduce = 1;
+  p.stage = heap_.local(ws_.stage[set]);
+  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn) * 4);
+  p.norm = norm.gamma != nullptr;
+  p.gamma = norm.gamma;
+  p.eps = norm.eps;
+  p.bcast = 0;
+  p.out[rank_] = D;
+  if (out_layout != nullptr) p.out_layout = *out_layout;
+  else p.out_layout.ld = g.N;
+  const char* why = nullptr;
+  check_launch(launch_fused(g, p, stream, &why), why, "gemm_reducescatter");
+  ++calls_;
+}
+
+StatusWord FusedEngine::read_status() {
+  StatusWord s{};
+  if (status_dev_ == nullptr) return s;
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  check(cudaMemcpy(&s, status_dev_, sizeof(s), cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+  return s;
+}
+
+void FusedEngine::clear_status() {
+  if (status_dev_ != nullptr) check(cudaMemset(status_dev_, 0, sizeof(StatusWord)), "cudaMemset(status)");
+}
+
+void FusedEngine::reset_counters() {
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  if (world_ > 1 && all_gather_) {
+    char t = 1;
+    std::vector<char> all(world_);
+    all_gather_(&t, 1, all.data());
+  }
+  if (heap_.valid()) {
+    for (int s = 0; s < 2; ++s) check(cudaMemset(flag_ptr(rank_, s), 0, kFlagWords * 4), "cudaMemset(counters)");
+    check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  }
+  if (world_ > 1 && all_gather_) {
+    char t = 1;
+    std::vector<char> all(world_);
+    all_gather_(&t, 1, all.data());
+  }
+  calls_ = 0;
+  clear_status();
+}
+
+std::string FusedEngine::describe(const StatusWord& s) {
+  static const char* names[] = {"ok",
+                                "a pipeline barrier inside the GEMM timed out",
+                                "partial results from a rank did not arrive in time",
+                                "all-reduce results from an owner did not arrive in time",
+                                "an index array held an out-of-range entry",
+                                "an all-gathered operand shard did not arrive in time"};
+  std::ostringstream os;
+  os << (s.code < 6 ? names[s.code] : "unknown") << " [code " << s.code << ", rank " << s.rank << ", where 0x"
+     << std::hex << s.where << std::dec << ", saw " << s.seen << ", wanted " << s.want << "]";
+  return os.str();
+}
+
+}  // namespace fo

@@ -1,0 +1,116 @@
+// FusedEngine: host-side orchestration of the fused sm_100a kernel.
+//
+// Owns the symmetric workspace (staging buffers for partial results, result
+// buffers for all-reduce, arrival counters), the device status word and the
+// per-call bookkeeping (which of the two staging/counter sets a call uses).
+// It plays the role of the reference's OverlapImpl host code
+// (reference: src/overlap_impl.cu:221-328) but issues exactly one kernel per
+// operation: no second stream, no wait kernels, no NCCL calls.
+//
+// Why two sets of staging buffers and counters are enough: a rank can finish
+// call i only after every rank has pushed its share of call i, hence after
+// every rank has finished call i-1.  A rank can therefore run at most one call
+// ahead of any other, so the set used by call i-1 is quiet when call i+1
+// starts, and the counters of the set used by call i+1 can be cleared by a
+// memset that is ordered on the stream before call i.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "../kernels/fused_params.h"
+#include "../kernels/gemm_launch.h"
+#include "symm_heap.h"
+
+namespace fo {
+
+struct NormArgs {
+  const void* gamma = nullptr;  // null = no RMSNorm
+  float eps = 1e-5f;
+};
+
+// Reference-compatible signalling for the plain GEMM (see FusedParams).
+struct SignalArgs {
+  int* seg_counter = nullptr;
+  const int* cseg = nullptr;
+  int nseg = 0;
+  int* ticket_counter = nullptr;
+  int* trace = nullptr;
+  const int* slot_of_tile = nullptr;
+};
+
+class FusedEngine {
+ public:
+  static constexpr int kMaxTileRows = 2048;
+
+  FusedEngine() = default;
+  ~FusedEngine();
+
+  void init(int rank, int world, AllGatherFn all_gather);
+  bool initialized() const { return status_dev_ != nullptr; }
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+
+  void set_timeout_ms(long long ms) { timeout_ns_ = static_cast<unsigned long long>(ms) * 1000000ull; }
+  void set_sm_count(int n) { sm_count_ = n; }
+  void set_raster_group(int g) { raster_group_ = g; }
+
+  // C[M,N] = A[M,K] * B[N,K]^T on this GPU only.  `layout` null = row-major.
+  void gemm(const GemmOperands& g, void* C, const OutLayout* layout, const SignalArgs* sig, cudaStream_t stream);
+
+  // GEMM + RMSNorm on one GPU (world size 1 form of the fused operations):
+  // `scratch` receives the un-normalised product, `out` the normalised rows.
+  void gemm_rmsnorm(const GemmOperands& g, void* scratch, void* out, const NormArgs& norm, cudaStream_t stream);
+
+  // Fused GEMM + all-reduce (+ RMSNorm).  Collective: every rank of the group
+  // must call it with the same shapes.  The result lands in a symmetric result
+  // buffer whose address is returned; if `out_user` is not null the result is
+  // also copied there (stream-ordered).  The returned buffer stays valid until
+  // the second next fused call on this engine.
+  void* gemm_allreduce(const GemmOperands& g, void* out_user, const NormArgs& norm, const OutLayout* out_layout,
+                       const SignalArgs* sig, cudaStream_t stream);
+
+  // Fused GEMM + reduce-scatter (+ RMSNorm) into D [M/world, N] (local memory).
+  // interleave = false: rank r receives rows [r*M/world, (r+1)*M/world).
+  // interleave = true : rank r receives rows r, r+world, r+2*world, ... (the
+  // ownership of the reference's scatter epilogue, reference:
+  // src/overlap/gemm_with_scatter.h:161-177, example/utils.py:24-52).
+  void gemm_reducescatter(const GemmOperands& g, void* D, bool interleave, const NormArgs& norm,
+                          const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream);
+
+  // Collective.  Makes sure the symmetric workspace can hold an M x N problem.
+  void ensure_workspace(long long m, long long n);
+
+  // Reads the device status word (synchronises the device).  code == ST_OK
+  // means no kernel has reported a failure since the last clear.
+  StatusWord read_status();
+  void clear_status();
+  // Collective; after a failed call: waits for the device, zeroes all counters.
+  void reset_counters();
+
+  static std::string describe(const StatusWord& s);
+
+ private:
+  struct Workspace {
+    size_t stage[2] = {0, 0};
+    size_t result[2] = {0, 0};
+    size_t flags[2] = {0, 0};  // kMaxTileRows arrival counters + 1 delivery counter each
+    long long capacity_elems = 0;
+  };
+  void base_params(FusedParams& p, const SignalArgs* sig);
+  uint32_t* flag_ptr(int rank, int set) const;
+  uint32_t* done_ptr(int rank, int set) const;
+
+  int rank_ = 0, world_ = 1;
+  AllGatherFn all_gather_;
+  SymmHeap heap_;
+  Workspace ws_;
+  StatusWord* status_dev_ = nullptr;
+  unsigned long long timeout_ns_ = 20000000000ull;
+  int sm_count_ = 0;
+  int raster_group_ = 0;  // 0 = choose per operation
+  unsigned long long calls_ = 0;  // fused collective calls issued so far
+};
+
+}  // namespace fo
