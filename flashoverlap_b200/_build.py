@@ -83,7 +83,11 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     nccl = sp / "nvidia" / "nccl"
     cublas = sp / "nvidia" / "cublas"
     include_paths = [str(_CSRC)]
-    ldflags = []
+    # Resolve the C++ runtime against the shared libstdc++ explicitly: a compiler
+    # wrapper whose own libstdc++.so link is broken would otherwise pull the
+    # exception runtime in statically, and a second copy of it in one process
+    # crashes as soon as an exception unwinds through this library.
+    ldflags = ["-L/usr/lib/x86_64-linux-gnu", "-l:libstdc++.so.6", "-l:libgcc_s.so.1"]
     if (nccl / "include" / "nccl.h").exists():
         include_paths.append(str(nccl / "include"))
         ldflags += [f"-L{nccl / 'lib'}", "-l:libnccl.so.2", f"-Wl,-rpath,{nccl / 'lib'}"]

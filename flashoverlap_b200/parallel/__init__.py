@@ -1,0 +1,8 @@
+"""Process-group bootstrap and construction of the communication objects."""
+from .bootstrap import (  # noqa: F401
+    broadcast_nccl_id,
+    init_distributed,
+    make_baseline_impl,
+    make_overlap_impl,
+    max_over_ranks,
+)

@@ -1,0 +1,106 @@
+"""One process per GPU: rendezvous, device binding and creation of the
+``OverlapImpl`` / ``BaselineImpl`` objects.
+
+The reference repeats this in every script (reference: tune/search.py:31-64,
+test/test.py:36-80): initialise ``torch.distributed`` from the environment,
+let rank 0 create an NCCL unique id, broadcast it as 16 int64 values and hand
+it to ``nccl_init``.  Here it lives in one place and also works on CPU with the
+``gloo`` backend (for the host-side logic and the tests that run without a GPU).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0):
+    """Initialise the default process group from RANK / WORLD_SIZE / MASTER_*.
+
+    Returns ``(rank, world_size, local_rank)``.  With a single process (no
+    ``WORLD_SIZE`` in the environment) nothing is initialised.
+    """
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local_rank % torch.cuda.device_count())
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        if backend is None:
+            backend = "nccl" if use_cuda else "gloo"
+        kwargs = {}
+        if backend == "nccl":
+            kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+        dist.init_process_group(
+            backend=backend,
+            rank=rank,
+            world_size=world,
+            timeout=datetime.timedelta(seconds=timeout_s),
+            **kwargs,
+        )
+    return rank, world, local_rank
+
+
+def _world(group=None):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def broadcast_nccl_id(group=None) -> list[int]:
+    """Rank 0 of ``group`` creates an NCCL unique id; everyone receives it as a
+    list of 16 ints (reference: tune/search.py:50-64)."""
+    rank, world = _world(group)
+    if world == 1:
+        return [0] * 16
+    device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else "cpu"
+    if rank == 0:
+        words = torch.ops.flashoverlap_op.generate_nccl_id()
+        t = torch.tensor(words, dtype=torch.int64, device=device)
+    else:
+        t = torch.zeros(16, dtype=torch.int64, device=device)
+    src = dist.get_global_rank(group, 0) if group is not None else 0
+    dist.broadcast(t, src=src, group=group)
+    return [int(v) for v in t.cpu().tolist()]
+
+
+def make_overlap_impl(group=None, timeout_ms: Optional[int] = None):
+    """An initialised ``OverlapImpl`` for the ranks of ``group`` (collective)."""
+    rank, world = _world(group)
+    impl = torch.classes.flashoverlap_class.OverlapImpl()
+    impl.nccl_init(rank, world, broadcast_nccl_id(group))
+    impl.cutlass_init()
+    impl.overlap_init()
+    env = os.environ.get("FLASHOVERLAP_TIMEOUT_MS")
+    if timeout_ms is None and env:
+        timeout_ms = int(env)
+    if timeout_ms is not None:
+        impl.set_timeout_ms(int(timeout_ms))
+    return impl
+
+
+def make_baseline_impl(group=None):
+    """An initialised ``BaselineImpl`` (cuBLAS + NCCL) for ``group`` (collective)."""
+    rank, world = _world(group)
+    impl = torch.classes.flashoverlap_class.BaselineImpl()
+    impl.nccl_init(rank, world, broadcast_nccl_id(group))
+    impl.cublas_init()
+    return impl
+
+
+def max_over_ranks(value: float, group=None) -> float:
+    """Maximum of a host number over the ranks (multi-GPU times are reported as
+    the slowest rank's, reference: test/test.py:205-207)."""
+    _, world = _world(group)
+    if world == 1:
+        return float(value)
+    device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else "cpu"
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())

@@ -1,0 +1,146 @@
+"""The fused kernel's reduce phase on one GPU (world size 1): GEMM + RMSNorm,
+all-reduce / reduce-scatter entry points degenerate to a local reduction, the
+reference-compatible reordered layout, the completion trace and RMSNorm ops.
+Oracle: PyTorch fp32."""
+import pytest
+import torch
+
+import flashoverlap_b200  # noqa: F401
+from flashoverlap_b200.utils.reorder import from_tile_order, reorder_indices, to_tile_order
+
+pytestmark = pytest.mark.gpu
+
+
+def rms_ref(x, w, eps):
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+
+def make_impl():
+    impl = torch.classes.flashoverlap_class.OverlapImpl()
+    impl.nccl_init(0, 1, [0] * 16)
+    impl.cutlass_init()
+    impl.overlap_init()
+    impl.set_timeout_ms(2000)
+    return impl
+
+
+def make_inputs(M, N, K, dtype, seed=0):
+    torch.manual_seed(seed)
+    A = torch.randn(M, K, device="cuda", dtype=dtype)
+    B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(dtype)
+    W = (1 + 0.1 * torch.randn(N, device="cuda")).to(dtype)
+    return A, B, W
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("algo", [0, 1, 2])
+def test_gemm_rmsnorm_single_kernel(dtype, algo):
+    M, N, K = 1024, 4096, 512
+    A, B, W = make_inputs(M, N, K, dtype)
+    C = torch.empty(M, N, device="cuda", dtype=dtype)
+    O = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)
+    impl = make_impl()
+    impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, algo)
+    torch.cuda.synchronize()
+    impl.check_status()
+    ref = A.float() @ B.float().t()
+    tol = 1e-2 if dtype == torch.float16 else 3e-2
+    assert (C.float() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    want = rms_ref(C, W, 1e-5)  # the kernel normalises the 16-bit product it stored
+    assert torch.isfinite(O.float()).all()
+    assert (O.float() - want).abs().max().item() <= tol * want.abs().max().item()
+
+
+@pytest.mark.parametrize("with_norm", [False, True])
+def test_world1_allreduce_and_reducescatter(with_norm):
+    M, N, K = 512, 2048, 256
+    A, B, W = make_inputs(M, N, K, torch.float16, seed=3)
+    impl = make_impl()
+    ref = A.float() @ B.float().t()
+    want = rms_ref(ref, W, 1e-5) if with_norm else ref
+    for _ in range(3):  # repeated calls alternate between the two buffer sets
+        out = impl.gemm_allreduce_fused(A, B, W if with_norm else None, 1e-5, 0)
+        torch.cuda.synchronize()
+        impl.check_status()
+        assert (out.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+    D = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16)
+    impl.gemm_reducescatter_fused(A, B, D, W if with_norm else None, 1e-5, 1, False)
+    torch.cuda.synchronize()
+    impl.check_status()
+    assert (D.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_compat_overlap_api_reordered_layout_and_trace():
+    M, N, K, algo = 1024, 2048, 256, 0
+    A, B, W = make_inputs(M, N, K, torch.float16, seed=5)
+    impl = make_impl()
+    bm, bn, _ = impl.algo_tile(algo)
+    tm, tn = M // bm, N // bn
+    tiles = tm * tn
+    hint = [(7 * i + 3) % tiles for i in range(tiles)]  # a permutation since gcd(7, 64) = 1
+    RA = reorder_indices(tiles, hint, device="cuda").reshape(tm, tn)
+    cseg_cpu = torch.tensor([16, 16, 32], dtype=torch.int32)
+    cseg_gpu = cseg_cpu.cuda()
+    MM = torch.zeros((tm + 1, tn), dtype=torch.int32, device="cuda")
+    C = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16)
+    impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, True)
+    torch.cuda.synchronize()
+    impl.check_status()
+    ref = A.float() @ B.float().t()
+    got = from_tile_order(C, bm, bn, RA)
+    assert (got.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+    # oracle for the layout itself
+    assert torch.equal(to_tile_order(got, bm, bn, RA), C)
+    flat = MM.flatten().cpu()
+    assert int(flat[tn - 1]) == tiles  # ticket counter
+    assert torch.equal(flat[tn:tn + tiles].sort().values, torch.arange(tiles, dtype=torch.int32))
+    assert int(flat[:tn - 1].abs().sum()) == 0  # segment counters end at zero
+    # reorder_rmsnorm undoes the layout
+    out = torch.empty_like(C)
+    torch.ops.flashoverlap_op.reorder_rmsnorm(C, out, W, bm, bn, 1, RA)
+    torch.cuda.synchronize()
+    want = rms_ref(got, W, 1e-5)
+    assert (out.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_compat_overlap_api_rejects_bad_segments():
+    M, N, K, algo = 256, 512, 64, 0
+    A, B, _ = make_inputs(M, N, K, torch.float16)
+    impl = make_impl()
+    RA = reorder_indices(4, [], device="cuda").reshape(2, 2)
+    MM = torch.zeros((1, 2), dtype=torch.int32, device="cuda")
+    C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    bad = torch.tensor([1, 1], dtype=torch.int32)  # sums to 2, not 4: the reference would spin forever
+    with pytest.raises(RuntimeError, match="sum"):
+        impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, bad, bad.cuda(), algo, False)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dim", [512, 4096, 8192, 16384, 32768, 1000 * 8])
+def test_rmsnorm_op(dtype, dim):
+    torch.manual_seed(0)
+    x = torch.randn(37, dim, device="cuda", dtype=dtype)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(dtype)
+    o = torch.empty_like(x)
+    torch.ops.flashoverlap_op.rmsnorm(x, o, w, 1e-6)
+    torch.cuda.synchronize()
+    want = rms_ref(x, w, 1e-6)
+    tol = 1e-2 if dtype == torch.float16 else 3e-2
+    assert (o.float() - want).abs().max().item() <= tol * want.abs().max().item()
+
+
+def test_reorder_rmsnorm_rldn2():
+    M, N, bm, bn = 512, 1024, 128, 256
+    tm, tn = M // bm, N // bn
+    torch.manual_seed(1)
+    x = torch.randn(M, N, device="cuda", dtype=torch.float16)
+    w = (1 + 0.1 * torch.randn(N, device="cuda")).half()
+    RA = reorder_indices(tm * tn, [5, 1, 9, 0], device="cuda").reshape(tm, tn)
+    for rldn in (1, 2, 4):
+        xr = to_tile_order(x, bm, bn, RA, rldn)
+        o = torch.empty_like(x)
+        torch.ops.flashoverlap_op.reorder_rmsnorm(xr, o, w, bm, bn, rldn, RA)
+        torch.cuda.synchronize()
+        want = rms_ref(x, w, 1e-5)
+        assert (o.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item(), f"rldn={rldn}"

@@ -1,0 +1,35 @@
+"""Runs the multi-GPU correctness worker under torchrun on every GPU of the
+node (2, 4 or 8); skipped on a single-GPU machine."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _world():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    for w in (8, 4, 2):
+        if n >= w:
+            return w
+    return 0
+
+
+@pytest.mark.timeout(900)
+def test_fused_ops_match_torch_semantics_on_all_gpus():
+    world = _world()
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ)
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "mgpu_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=850)
+    tail = "\n".join((res.stdout + "\n" + res.stderr).splitlines()[-60:])
+    assert res.returncode == 0, tail
+    assert "DONE failures=0" in res.stdout, tail
