@@ -1,0 +1,128 @@
+"""Row-parallel linear layers: the K dimension of ``x @ W^T`` is split over
+the ranks and the partial products are summed by an all-reduce or a
+reduce-scatter (reference: example/RowParallelLinear.py:11-85).
+
+* :class:`RowParallelLayer` is the PyTorch golden path (matmul + collective).
+* :class:`OverlapRowParallelLayer` keeps the reference's constructor and
+  tile-reordered output so that its scripts and tuned configs work unchanged.
+* :class:`FusedRowParallelLinear` is the native interface: natural-order output,
+  optional fused RMSNorm, contiguous or interleaved reduce-scatter.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..utils.reorder import div_up, generate_row_mapping, reorder_indices
+
+
+def _device(device):
+    if device is not None:
+        return torch.device(device)
+    return torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu")
+
+
+class RowParallelLayer(nn.Module):
+    def __init__(self, in_features: int, out_features: int, comm_op: str, tp_group=None, dtype=torch.float16,
+                 device=None):
+        super().__init__()
+        assert comm_op in ("all_reduce", "reduce_scatter"), f"unknown comm_op {comm_op!r}"
+        self.tp_group = tp_group
+        self.comm_op = comm_op
+        self.weight = nn.Parameter(torch.randn(out_features, in_features, dtype=dtype, device=_device(device)))
+
+    def forward(self, x):
+        out = torch.matmul(x, self.weight.t())
+        if not (dist.is_available() and dist.is_initialized()):
+            return out
+        if self.comm_op == "all_reduce":
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.tp_group)
+            return out
+        world = dist.get_world_size(self.tp_group)
+        cout = torch.empty((x.size(0) // world, self.weight.size(0)), dtype=out.dtype, device=out.device)
+        dist.reduce_scatter_tensor(cout, out, group=self.tp_group)
+        return cout
+
+
+class OverlapRowParallelLayer(nn.Module):
+    """Reference-compatible layer.  ``config`` is a stage-2 tuning result
+    (``BM``, ``BN``, ``Algo``, ``hint``, ``cSeg``); ``nccl_id`` the 16-word id
+    broadcast from rank 0.  The all-reduce output is in tile-reordered layout
+    (feed it to :class:`ReorderRMSNorm`); the reduce-scatter output holds this
+    rank's interleaved rows in the same slot order."""
+
+    def __init__(self, rank: int, world_size: int, in_features: int, out_features: int, M: int, config: dict,
+                 comm_op: str, nccl_id, dtype=torch.float16, device=None):
+        super().__init__()
+        assert comm_op in ("all_reduce", "reduce_scatter"), f"unknown comm_op {comm_op!r}"
+        dev = _device(device)
+        self.weight = nn.Parameter(torch.randn(out_features, in_features, dtype=dtype, device=dev))
+        self.world_size = world_size
+        self.comm_op = comm_op
+        self.overlap_class = torch.classes.flashoverlap_class.OverlapImpl()
+        self.overlap_class.nccl_init(rank, world_size, [int(v) for v in nccl_id])
+        self.overlap_class.cutlass_init()
+        self.overlap_class.overlap_init()
+        BM, BN = config["BM"], config["BN"]
+        hint, cseg = config["hint"], config["cSeg"]
+        tm, tn = div_up(M, BM), div_up(out_features, BN)
+        self.algo = config["Algo"]
+        self.counter = torch.zeros((1, max(tn, len(cseg))), dtype=torch.int32, device=dev)
+        self.reorder_array = reorder_indices(tm * tn, hint, device=dev).reshape(tm, tn)
+        self.cseg_cpu = torch.tensor(cseg, dtype=torch.int32)
+        self.cseg_gpu = self.cseg_cpu.to(dev)
+        self.row_array = (generate_row_mapping(M, out_features, BM, BN, cseg, world_size, device=dev)
+                          if comm_op == "reduce_scatter" else None)
+
+    def forward(self, x):
+        n = self.weight.size(0)
+        if self.comm_op == "all_reduce":
+            out = torch.empty((x.size(0), n), dtype=x.dtype, device=x.device)
+            self.overlap_class.gemm_allreduce_overlap(x, self.weight, out, self.counter, self.reorder_array, 1,
+                                                      self.cseg_cpu, self.cseg_gpu, self.algo, False)
+            return out
+        tmp = torch.empty((x.size(0), n), dtype=x.dtype, device=x.device)
+        out = torch.empty((x.size(0) // self.world_size, n), dtype=x.dtype, device=x.device)
+        self.overlap_class.gemm_reducescatter_overlap(x, self.weight, tmp, out, self.counter, self.reorder_array,
+                                                      self.row_array, 1, self.cseg_cpu, self.cseg_gpu, self.algo,
+                                                      False)
+        return out
+
+
+class FusedRowParallelLinear(nn.Module):
+    """``y = collective(x @ W^T)`` with an optional RMSNorm, as one kernel.
+
+    ``impl`` is an initialised ``OverlapImpl`` (see
+    :func:`flashoverlap_b200.parallel.make_overlap_impl`); ``norm_weight`` turns
+    the fused RMSNorm on.  With ``comm_op="all_reduce"`` the returned tensor
+    aliases the implementation's symmetric result buffer and stays valid until
+    the second next fused call on the same ``impl``."""
+
+    def __init__(self, impl, in_features: int, out_features: int, comm_op: str = "all_reduce",
+                 norm: bool = False, eps: float = 1e-5, algo: int = 0, interleave: bool = False,
+                 dtype=torch.float16, device=None):
+        super().__init__()
+        assert comm_op in ("all_reduce", "reduce_scatter"), f"unknown comm_op {comm_op!r}"
+        dev = _device(device)
+        self.impl = impl
+        self.comm_op = comm_op
+        self.eps = eps
+        self.algo = algo
+        self.interleave = interleave
+        self.world_size = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        self.weight = nn.Parameter(torch.randn(out_features, in_features, dtype=dtype, device=dev) /
+                                   (in_features * self.world_size) ** 0.5)
+        self.norm_weight: Optional[nn.Parameter] = (
+            nn.Parameter(torch.ones(out_features, dtype=dtype, device=dev)) if norm else None)
+
+    @torch.no_grad()
+    def forward(self, x):
+        if self.comm_op == "all_reduce":
+            return self.impl.gemm_allreduce_fused(x, self.weight, self.norm_weight, self.eps, self.algo)
+        out = torch.empty((x.size(0) // self.world_size, self.weight.size(0)), dtype=x.dtype, device=x.device)
+        self.impl.gemm_reducescatter_fused(x, self.weight, out, self.norm_weight, self.eps, self.algo,
+                                           self.interleave)
+        return out
