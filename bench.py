@@ -60,7 +60,7 @@ def main():
     from flashoverlap_b200.models import FusedRowParallelLinear
     from flashoverlap_b200.parallel import init_distributed, make_baseline_impl, make_overlap_impl, max_over_ranks
     from flashoverlap_b200.utils.clocks import ClockSampler
-    from flashoverlap_b200.utils.timing import flush_l2, time_steps
+    from flashoverlap_b200.utils.timing import time_steps
 
     if not torch.cuda.is_available():
         print(json.dumps({"error": "bench.py needs a CUDA device"}))
@@ -193,7 +193,8 @@ def main():
                 "algo": args.algo,
             },
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
-                       "power_w_max": clocks["power_w_max"], "samples": clocks["samples"]},
+                       "power_w_max": clocks["power_w_max"], "samples": clocks["samples"],
+                       "samples_under_load": clocks["samples_under_load"]},
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 5),
                     "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
                     "d2h_bytes_per_step": row_host.numel() * row_host.element_size(),

@@ -122,6 +122,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)
+      .def("set_phase_trace", &OverlapImpl::SetPhaseTrace)
       .def("status", &OverlapImpl::Status)
       .def("status_string", &OverlapImpl::StatusString)
       .def("check_status", &OverlapImpl::CheckStatus)

@@ -369,6 +369,17 @@ void OverlapImpl::SetTimeoutMs(int64_t ms) {
 }
 void OverlapImpl::SetSmCount(int64_t n) { engine_.set_sm_count(static_cast<int>(n)); }
 void OverlapImpl::SetRasterGroup(int64_t g) { engine_.set_raster_group(static_cast<int>(g)); }
+void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
+  if (buf.numel() == 0) {
+    engine_.set_phase_trace(nullptr);
+    phase_trace_ = at::Tensor();
+    return;
+  }
+  TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && buf.scalar_type() == at::kLong, "trace buffer must be a contiguous CUDA int64 tensor");
+  TORCH_CHECK(buf.numel() >= 4 * device_sm_count(), "trace buffer needs 4 entries per SM (", 4 * device_sm_count(), ")");
+  phase_trace_ = buf;  // keeps the memory alive
+  engine_.set_phase_trace(reinterpret_cast<unsigned long long*>(buf.data_ptr<int64_t>()));
+}
 
 std::vector<int64_t> OverlapImpl::Status() {
   StatusWord s = engine_.read_status();

@@ -57,6 +57,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   void SetTimeoutMs(int64_t ms);
   void SetSmCount(int64_t n);
   void SetRasterGroup(int64_t g);
+  // Every following launch records per-CTA phase timestamps into `buf`
+  // (int64, at least 4 * SM count entries; an empty tensor turns it off).
+  void SetPhaseTrace(at::Tensor buf);
   // [code, rank, where, seen, want]; code 0 = no failure reported.
   std::vector<int64_t> Status();
   std::string StatusString();
@@ -73,6 +76,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   Communicator comm_;
   FusedEngine engine_;
   bool engine_ready_ = false;
+  at::Tensor phase_trace_;
 };
 
 }  // namespace fo

@@ -100,6 +100,11 @@ struct alignas(64) FusedParams {
   uint32_t* done[kMaxRanks];       // per-rank "rows delivered" counter (all-reduce)
   uint32_t done_target;
 
+  // ---- phase trace ----------------------------------------------------------
+  // Optional: per CTA {kernel start, end of the GEMM phase, end of the reduce
+  // phase, tiles computed} as %globaltimer nanoseconds, 4 x uint64 per CTA.
+  unsigned long long* phase_trace;
+
   // ---- failure reporting ----------------------------------------------------
   StatusWord* status;
   unsigned long long timeout_ns;

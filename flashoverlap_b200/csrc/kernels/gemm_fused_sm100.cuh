@@ -8,9 +8,11 @@
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma / tcgen05.commit)
 //   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end)
 //   warp 3      idle during the GEMM phase
+// With CTAS == 2 two such CTAs form a cluster: both stage operands and run an
+// epilogue for their own 128 rows, the MMA warp of rank 0 issues for the pair.
 //   warps 4-7   epilogue       (tcgen05.ld -> convert -> smem transpose ->
 //                               coalesced 16-byte stores -> arrival counter)
-// After its last tile the whole CTA joins the reduce phase (row-per-CTA).
+// After its last tile the whole CTA joins the reduce phase (one row per warp).
 //
 // Replaces, as one launch, the reference's signalling GEMM + wait kernel +
 // segmented NCCL calls (reference: src/overlap_impl.cu:221-328).
@@ -21,14 +23,21 @@
 
 namespace fo {
 
-template <int BN_>
+// CTAS == 1: one CTA computes a 128 x BN tile (tcgen05.mma.cta_group::1).
+// CTAS == 2: a cluster of two CTAs computes a 256 x BN tile with
+//   tcgen05.mma.cta_group::2; each CTA stages its own 128 rows of A and one
+//   half of the B tile, so every SM fetches a third less per FLOP.
+template <int BN_, int CTAS_ = 1>
 struct TileTraits {
-  static constexpr int BM = 128;
+  static constexpr int CTAS = CTAS_;
+  static constexpr int BM = 128;           // rows per CTA
+  static constexpr int TILE_M = BM * CTAS;  // rows per tile
   static constexpr int BN = BN_;
   static constexpr int BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
   static constexpr int UMMA_K = 16;
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = BN / CTAS;  // rows of B staged by each CTA
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_WARPS = 4;
   static constexpr int EPI_SLAB_BYTES = 32 * 128;  // 32 rows x 64 columns of 16-bit values
@@ -40,11 +49,11 @@ struct TileTraits {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; power of two >= 32
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+  static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
   static_assert(STAGES >= 3, "pipeline too shallow");
 };
 
 constexpr int kThreads = 256;
-constexpr int kMaxRowChunksPerThread = 8;  // reduce phase: N <= 8 * 256 * 8 = 16384
 
 // ---------------------------------------------------------------------------
 // helpers
@@ -121,12 +130,183 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
 }
 
 // ---------------------------------------------------------------------------
+// reduce phase: one warp per owned row
+// ---------------------------------------------------------------------------
+// Each warp of the CTA takes one row at a time: it waits (bounded) until the
+// partial rows of every rank have arrived, sums them in fp32 and rounds the
+// sum to the 16-bit type (the value an all-reduce would have produced).
+// Without RMSNorm the rounded sum goes straight to its destination(s); with
+// RMSNorm it is parked in shared memory while the warp accumulates the sum of
+// squares, then scaled, multiplied by the weight and written out.  Warps never
+// synchronise with one another, so every SM keeps several independent chains
+// of loads in flight.  WS > 0 fixes the number of ranks at compile time (all
+// loads of a batch are issued before the first use); WS == 0 is the generic
+// fallback for other group sizes.
+template <bool BF16, int WS>
+__device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem, int smem_bytes, int warp, int lane,
+                                             uint64_t deadline, volatile uint32_t* abort_flag) {
+  constexpr int BM = 128;
+  constexpr int U = WS == 0 ? 1 : (WS == 1 ? 8 : (WS == 2 ? 4 : 2));  // chunks per lane per batch
+  constexpr int NS = WS == 0 ? kMaxRanks : WS;
+  const int ws = WS == 0 ? p.ws : WS;
+  const int n_chunks = p.N >> 3;  // 16-byte chunks per row
+  const int row_bytes = p.N * 2;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+
+  // RMSNorm: the weight vector is staged in shared memory once per CTA, then
+  // one row buffer per active warp follows it.
+  int rows_per_iter = kThreads / 32;
+  if (p.norm) {
+    const uint16_t* gamma = reinterpret_cast<const uint16_t*>(p.gamma);
+    for (int c = threadIdx.x; c < n_chunks; c += kThreads) {
+      ptx::st_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4), *reinterpret_cast<const uint4*>(gamma + c * 8));
+    }
+    const int fit = (smem_bytes - row_bytes) / row_bytes;
+    if (fit < rows_per_iter) rows_per_iter = fit;
+    __syncthreads();
+  }
+  if (rows_per_iter < 1 || warp >= rows_per_iter) return;  // (< 1 is rejected on the host)
+  const uint32_t gbuf = smem_base;
+  const uint32_t rowbuf = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(warp + 1);
+  const int rows_local = p.rows_per_owner;
+  const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
+  const long long src_stride = static_cast<long long>(rows_local) * p.N;
+  const uint32_t* my_flag = p.flag[p.me];
+
+  auto load_batch = [&](uint4 (&v)[U][NS], const uint16_t* src0, int c0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < n_chunks) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+          if (s < ws) v[u][s] = ptx::ld_cg_v4(src0 + s * src_stride + c * 8);
+        }
+      }
+    }
+  };
+  auto store_out = [&](int out_row, int c, const uint4& o) {
+    const long long off = layout_offset(p.out_layout, out_row, c * 8);
+    if (p.bcast) {
+#pragma unroll
+      for (int r = 0; r < NS; ++r) {
+        if (r < ws) {
+          int d = p.me + 1 + r;  // start with the next rank: owners spread over destinations
+          if (d >= ws) d -= ws;
+          ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[d]) + off, o);
+        }
+      }
+    } else {
+      ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[p.me]) + off, o);
+    }
+  };
+
+  for (int i = 0;; ++i) {
+    const int lr = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (warp + rows_per_iter * i);
+    if (lr >= rows_local) break;
+    int g;  // global row
+    if (p.own_mode == OWN_BLOCK) g = p.me * rows_local + lr;
+    else if (p.own_mode == OWN_INTERLEAVE) g = lr * ws + p.me;
+    else g = lr;
+    const int rb = g / BM;
+
+    // wait until every rank's partials for tile row rb have arrived
+    uint32_t ok = 1;
+    if (lane == 0) {
+      uint32_t seen = 0;
+      if (!ptx::wait_counter_geq(my_flag + rb, p.flag_target, deadline, &seen)) {
+        report_error(p.status, ST_TIMEOUT_FLAG, p.me, rb, seen, p.flag_target);
+        *abort_flag = 1;
+        ok = 0;
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) break;
+
+    const int out_row = p.bcast ? g : lr;
+    const uint16_t* src0 = stage + static_cast<long long>(lr) * p.N;
+    float ssq = 0.f;
+    // software pipeline: the loads of batch k+1 are in flight while batch k is summed
+    uint4 cur[U][NS], nxt[U][NS];
+    load_batch(cur, src0, lane);
+    for (int c0 = lane; c0 < n_chunks; c0 += 32 * U) {
+      if (c0 + 32 * U < n_chunks) load_batch(nxt, src0, c0 + 32 * U);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < n_chunks) {
+          float a[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < NS; ++s) {
+            if (s < ws) {
+              float2 f;
+              f = unpack2<BF16>(cur[u][s].x); a[0] += f.x; a[1] += f.y;
+              f = unpack2<BF16>(cur[u][s].y); a[2] += f.x; a[3] += f.y;
+              f = unpack2<BF16>(cur[u][s].z); a[4] += f.x; a[5] += f.y;
+              f = unpack2<BF16>(cur[u][s].w); a[6] += f.x; a[7] += f.y;
+            }
+          }
+          uint4 h;
+          h.x = pack2<BF16>(a[0], a[1]);
+          h.y = pack2<BF16>(a[2], a[3]);
+          h.z = pack2<BF16>(a[4], a[5]);
+          h.w = pack2<BF16>(a[6], a[7]);
+          if (p.norm) {
+            float2 f;
+            f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
+            f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
+            f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
+            f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
+            ptx::st_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4), h);
+          } else {
+            store_out(out_row, c, h);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int s = 0; s < NS; ++s) cur[u][s] = nxt[u][s];
+      }
+    }
+    if (p.norm) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+      const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
+      // each lane re-reads exactly the chunks it wrote, so no warp barrier is needed
+#pragma unroll 4
+      for (int c = lane; c < n_chunks; c += 32) {
+        const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
+        const uint4 w = ptx::ld_shared_v4(gbuf + (static_cast<uint32_t>(c) << 4));
+        float2 f;
+        uint4 o;
+        f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
+        f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
+        f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
+        f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
+        store_out(out_row, c, o);
+      }
+    }
+    if (p.bcast) {
+      __syncwarp();  // every lane's stores of this row precede the releases below
+      if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <int BN, bool BF16>
+template <int BN, bool BF16, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __grid_constant__ FusedParams p) {
-  using T = TileTraits<BN>;
-  constexpr int BM = T::BM, BK = T::BK, STAGES = T::STAGES;
+  using T = TileTraits<BN, CTAS>;
+  constexpr int BM = T::BM, BK = T::BK, STAGES = T::STAGES, TILE_M = T::TILE_M;
+  // rank inside the CTA pair; rank 0 (the leader) issues the MMAs of the pair
+  const uint32_t cta_rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
+  const int first_tile = static_cast<int>(blockIdx.x) / CTAS;
+  const int tile_stride = static_cast<int>(gridDim.x) / CTAS;
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle of TMA and UMMA.
@@ -141,11 +321,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  float* red_buf = reinterpret_cast<float*>(tmem_slot + 2);  // [8] block-reduce scratch
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint64_t deadline = ptx::globaltimer_ns() + p.timeout_ns;
+  const uint64_t t_start = ptx::globaltimer_ns();
+  const uint64_t deadline = t_start + p.timeout_ns;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -154,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&tfull_bar[i], 1);
-      ptx::mbar_init(&tempty_bar[i], T::EPI_WARPS);
+      ptx::mbar_init(&tempty_bar[i], T::EPI_WARPS * CTAS);  // the leader hears from both epilogues
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -165,11 +345,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     ptx::prefetch_tensormap(&p.tmB);
   }
   if (warp == 2) {
-    ptx::tmem_alloc(tmem_slot, T::TMEM_COLS);
-    ptx::tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      ptx::tmem_alloc_pair(tmem_slot, T::TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, T::TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) ptx::cluster_sync();  // both CTAs' barriers exist before anyone signals across
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -182,14 +368,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         int m_blk, n_blk;
         tile_coords(p, t, m_blk, n_blk);
+        const int a_row = m_blk * TILE_M + static_cast<int>(cta_rank) * BM;
+        const int b_row = n_blk * BN + static_cast<int>(cta_rank) * T::B_ROWS;
         if (p.a_ready != nullptr) {
           // All-gathered A: rows of this tile come from one source rank; wait
           // until that shard has landed in local memory, then order the
           // generic-proxy arrival before the async-proxy (TMA) reads.
-          const int src = (m_blk * BM) / p.a_rows_per_rank;
+          const int src = a_row / p.a_rows_per_rank;
           uint32_t seen = 0;
           if (!ptx::wait_counter_geq(p.a_ready + src, p.a_ready_target, deadline, &seen)) {
             report_error(p.status, ST_TIMEOUT_GATHER, p.me, src, seen, p.a_ready_target);
@@ -206,9 +394,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
             ok = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
-          ptx::tma_load_2d(smem_a + stage * T::A_BYTES, &p.tmA, &full_bar[stage], kb * BK, m_blk * BM);
-          ptx::tma_load_2d(smem_b + stage * T::B_BYTES, &p.tmB, &full_bar[stage], kb * BK, n_blk * BN);
+          if constexpr (CTAS == 2) {
+            // both CTAs' bytes are counted on the leader's barrier
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * T::STAGE_BYTES);
+            ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES, &p.tmA, &full_bar[stage], kb * BK, a_row);
+            ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES, &p.tmB, &full_bar[stage], kb * BK, b_row);
+          } else {
+            ptx::mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
+            ptx::tma_load_2d(smem_a + stage * T::A_BYTES, &p.tmA, &full_bar[stage], kb * BK, a_row);
+            ptx::tma_load_2d(smem_b + stage * T::B_BYTES, &p.tmB, &full_bar[stage], kb * BK, b_row);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -223,13 +418,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_f16(BF16 ? 1 : 0, BM, BN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(BF16 ? 1 : 0, TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
         if (!ptx::mbar_wait(&tempty_bar[buf], (use & 1u) ^ 1u, deadline)) {
@@ -253,15 +448,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
 #pragma unroll
           for (int k = 0; k < BK / T::UMMA_K; ++k) {
             // advancing K by 16 elements = 32 bytes = 2 descriptor address units
-            ptx::umma_f16_ss(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CTAS == 2) ptx::umma_f16_ss_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else ptx::umma_f16_ss(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(&empty_bar[stage]);  // frees the stage once the MMAs have read it
+          // frees the stage (in both CTAs of a pair) once the MMAs have read it
+          if constexpr (CTAS == 2) ptx::umma_commit_pair(&empty_bar[stage], 3);
+          else ptx::umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) ptx::umma_commit(&tfull_bar[buf]);  // accumulator complete
+        if (ok) {  // accumulator complete
+          if constexpr (CTAS == 2) ptx::umma_commit_pair(&tfull_bar[buf], 3);
+          else ptx::umma_commit(&tfull_bar[buf]);
+        }
       }
     }
   } else if (warp >= 4) {
@@ -270,7 +471,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     const uint32_t slab = ptx::smem_u32(smem_epi + q * T::EPI_SLAB_BYTES);
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    // the accumulator-free barrier lives in the leader CTA of a pair
+    const uint32_t tempty_addr0 = CTAS == 2 ? ptx::mapa_shared(ptx::smem_u32(&tempty_bar[0]), 0) : 0u;
+    for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
       int m_blk, n_blk;
       tile_coords(p, t, m_blk, n_blk);
       const int buf = it & 1;
@@ -285,7 +488,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       }
       ptx::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
-      const int row0 = m_blk * BM + q * 32;  // first global row of this warp's slab
+      const int row0 = m_blk * TILE_M + static_cast<int>(cta_rank) * BM + q * 32;  // first global row of this warp's slab
+      const int flag_blk = row0 / BM;  // 128-row block the arrival counters are kept for
 
 #pragma unroll 1
       for (int cc = 0; cc < BN / 64; ++cc) {
@@ -297,7 +501,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           // accumulator fully read: hand the TMEM buffer back to the MMA warp
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&tempty_bar[buf]);
+          if (lane == 0) {
+            if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tempty_addr0 + 8u * buf);
+            else ptx::mbar_arrive(&tempty_bar[buf]);
+          }
         }
         // registers -> swizzled smem slab (row = lane, 8 chunks of 16 bytes)
 #pragma unroll
@@ -349,14 +556,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         // __syncwarp above ordered every lane's stores before this point; the
         // release on the reduction publishes them at system scope.
         if (p.own_mode == OWN_INTERLEAVE) {
-          if (lane < p.ws) ptx::red_release_sys_add(p.flag[lane] + m_blk, 1u);
+          if (lane < p.ws) ptx::red_release_sys_add(p.flag[lane] + flag_blk, 1u);
         } else if (p.own_mode == OWN_BLOCK) {
-          if (lane == 0) ptx::red_release_sys_add(p.flag[row0 / p.rows_per_owner] + m_blk, 1u);
+          if (lane == 0) ptx::red_release_sys_add(p.flag[row0 / p.rows_per_owner] + flag_blk, 1u);
         } else {
-          if (lane == 0) ptx::red_release_sys_add(p.flag[0] + m_blk, 1u);
+          if (lane == 0) ptx::red_release_sys_add(p.flag[0] + flag_blk, 1u);
         }
       }
-      if (q == 0 && lane == 0 && (p.seg_counter != nullptr || p.ticket_counter != nullptr)) {
+      if (q == 0 && lane == 0 && cta_rank == 0 && (p.seg_counter != nullptr || p.ticket_counter != nullptr)) {
         // Reference-compatible bookkeeping, once per tile.  (The three other
         // epilogue warps of this tile may still be storing; consumers of these
         // counters run after the kernel, in stream order.)
@@ -382,118 +589,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   // ===================== teardown of the GEMM phase =====================
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) ptx::cluster_sync();  // the partner may still read this CTA's operands / signal its barriers
   if (warp == 2) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+    if constexpr (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, T::TMEM_COLS);
+    else ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+  }
+  if (p.phase_trace != nullptr && threadIdx.x == 0) {
+    unsigned long long* tr = p.phase_trace + 4ull * blockIdx.x;
+    tr[0] = t_start;
+    tr[1] = ptx::globaltimer_ns();
+    tr[2] = 0;
+    int mine = 0;
+    for (int t = first_tile; t < num_tiles; t += tile_stride) ++mine;
+    tr[3] = static_cast<unsigned long long>(mine);
   }
   if (!p.reduce || *abort_flag) return;
 
   // ===================== reduce phase =====================
-  // One CTA per owned row: sum the ws partial rows in fp32, optionally
-  // RMS-normalise, write the row to its destination(s).
-  const int n_chunks = p.N / 8;  // 16-byte chunks per row
-  const int rows_local = p.rows_per_owner;
-  const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
-  const long long src_stride = static_cast<long long>(rows_local) * p.N;
-  const uint32_t* my_flag = p.flag[p.me];
+  ptx::fence_proxy_async_smem();  // the pipeline's shared memory is reused through the generic proxy
+  switch (p.ws) {
+    case 1: reduce_phase<BF16, 1>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+    case 2: reduce_phase<BF16, 2>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+    case 4: reduce_phase<BF16, 4>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+    case 8: reduce_phase<BF16, 8>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+    default: reduce_phase<BF16, 0>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+  }
 
-  for (int lr = blockIdx.x; lr < rows_local; lr += gridDim.x) {
-    int g;  // global row
-    if (p.own_mode == OWN_BLOCK) g = p.me * rows_local + lr;
-    else if (p.own_mode == OWN_INTERLEAVE) g = lr * p.ws + p.me;
-    else g = lr;
-    const int rb = g / BM;
-
-    // wait until every rank's partials for tile row rb have arrived
-    if (threadIdx.x == 0) {
-      uint32_t seen = 0;
-      if (!ptx::wait_counter_geq(my_flag + rb, p.flag_target, deadline, &seen)) {
-        report_error(p.status, ST_TIMEOUT_FLAG, p.me, rb, seen, p.flag_target);
-        *abort_flag = 1;
-      }
-    }
-    __syncthreads();
-    if (*abort_flag) return;
-
-    float acc[kMaxRowChunksPerThread][8];
-    float ssq = 0.f;
-#pragma unroll
-    for (int k = 0; k < kMaxRowChunksPerThread; ++k) {
-      const int c = threadIdx.x + k * kThreads;
-      if (c < n_chunks) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
-        const uint16_t* src = stage + static_cast<long long>(lr) * p.N + c * 8;
-        uint4 v[kMaxRanks];
-#pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s) {
-          if (s < p.ws) v[s] = ptx::ld_cg_v4(src + s * src_stride);
-        }
-#pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s) {
-          if (s < p.ws) {
-            float2 f;
-            f = unpack2<BF16>(v[s].x); acc[k][0] += f.x; acc[k][1] += f.y;
-            f = unpack2<BF16>(v[s].y); acc[k][2] += f.x; acc[k][3] += f.y;
-            f = unpack2<BF16>(v[s].z); acc[k][4] += f.x; acc[k][5] += f.y;
-            f = unpack2<BF16>(v[s].w); acc[k][6] += f.x; acc[k][7] += f.y;
-          }
-        }
-        if (p.norm) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) ssq += acc[k][e] * acc[k][e];
-        }
-      }
-    }
-    float rstd = 1.f;
-    if (p.norm) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-      if (lane == 0) red_buf[warp] = ssq;
-      __syncthreads();
-      float tot = 0.f;
-#pragma unroll
-      for (int w = 0; w < kThreads / 32; ++w) tot += red_buf[w];
-      rstd = rsqrtf(tot / static_cast<float>(p.N) + p.eps);
-    }
-    const int out_row = p.bcast ? g : lr;
-#pragma unroll
-    for (int k = 0; k < kMaxRowChunksPerThread; ++k) {
-      const int c = threadIdx.x + k * kThreads;
-      if (c < n_chunks) {
-        uint4 v;
-        if (p.norm) {
-          const uint4 w = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.gamma) + c * 8);
-          v.x = norm_pack2<BF16>(acc[k][0], acc[k][1], rstd, w.x);
-          v.y = norm_pack2<BF16>(acc[k][2], acc[k][3], rstd, w.y);
-          v.z = norm_pack2<BF16>(acc[k][4], acc[k][5], rstd, w.z);
-          v.w = norm_pack2<BF16>(acc[k][6], acc[k][7], rstd, w.w);
-        } else {
-          v.x = pack2<BF16>(acc[k][0], acc[k][1]);
-          v.y = pack2<BF16>(acc[k][2], acc[k][3]);
-          v.z = pack2<BF16>(acc[k][4], acc[k][5]);
-          v.w = pack2<BF16>(acc[k][6], acc[k][7]);
-        }
-        const long long off = layout_offset(p.out_layout, out_row, c * 8);
-        if (p.bcast) {
-          for (int r = 0; r < p.ws; ++r) {
-            // start with the next rank so that the eight owners do not all
-            // write to the same destination at the same moment
-            int d = p.me + 1 + r;
-            if (d >= p.ws) d -= p.ws;
-            ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[d]) + off, v);
-          }
-        } else {
-          ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[p.me]) + off, v);
-        }
-      }
-    }
-    if (p.bcast) {
-      __syncthreads();  // every thread's stores of this row precede the releases below
-      if (threadIdx.x < p.ws && p.done[threadIdx.x] != nullptr) ptx::red_release_sys_add(p.done[threadIdx.x], 1u);
-    } else if (p.norm) {
-      __syncthreads();  // red_buf is reused by the next row
-    }
+  if (p.phase_trace != nullptr && lane == 0) {
+    atomicMax(p.phase_trace + 4ull * blockIdx.x + 2, static_cast<unsigned long long>(ptx::globaltimer_ns()));
   }
 
   // All-reduce: the kernel may only end once every owner has delivered its

@@ -46,10 +46,10 @@ bool make_tensor_map(CUtensorMap* map, const void* base, int rows, int cols, int
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, int CTAS>
 cudaError_t launch_instance(const FusedParams& p, int grid, cudaStream_t stream) {
-  using T = TileTraits<BN>;
-  auto kern = gemm_fused_sm100_kernel<BN, BF16>;
+  using T = TileTraits<BN, CTAS>;
+  auto kern = gemm_fused_sm100_kernel<BN, BF16, CTAS>;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -58,8 +58,24 @@ cudaError_t launch_instance(const FusedParams& p, int grid, cudaStream_t stream)
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  kern<<<grid, kThreads, T::SMEM_BYTES, stream>>>(p);
-  return cudaGetLastError();
+  if (CTAS == 1) {
+    kern<<<grid, kThreads, T::SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+  }
+  // CTA pairs: a cluster of two CTAs per tile
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = T::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 }  // namespace
@@ -85,15 +101,16 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
     return cudaErrorInvalidValue;
   }
   if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.M % tc.bm != 0 || g.N % tc.bn != 0 || g.K % 8 != 0) {
-    *why = "shape not supported: need M % 128 == 0, N % tile_n == 0, K % 8 == 0";
+    *why = "shape not supported: need M % tile_m == 0, N % tile_n == 0, K % 8 == 0";
     return cudaErrorInvalidValue;
   }
   if ((reinterpret_cast<uintptr_t>(g.A) & 15u) || (reinterpret_cast<uintptr_t>(g.B) & 15u)) {
     *why = "A and B must be 16-byte aligned";
     return cudaErrorInvalidValue;
   }
-  if (!make_tensor_map(&p.tmA, g.A, g.M, g.K, tc.bm, g.dtype) ||
-      !make_tensor_map(&p.tmB, g.B, g.N, g.K, tc.bn, g.dtype)) {
+  // every CTA stages 128 rows of A and (for a CTA pair) half of the B tile
+  if (!make_tensor_map(&p.tmA, g.A, g.M, g.K, 128, g.dtype) ||
+      !make_tensor_map(&p.tmB, g.B, g.N, g.K, tc.bn / tc.ctas, g.dtype)) {
     *why = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
@@ -105,22 +122,29 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
   if (p.raster_group <= 0) p.raster_group = 1;
   if (p.raster_group > p.TM) p.raster_group = p.TM;
   if (p.rot < 0 || p.rot >= p.TM) p.rot = 0;
-  if (p.reduce && g.N > kMaxRowChunksPerThread * kThreads * 8) {
-    *why = "fused reduce phase supports N <= 16384";
+  if (p.reduce && p.norm && static_cast<long long>(g.N) * 4 > TileTraits<256, 1>::STAGES * TileTraits<256, 1>::STAGE_BYTES + TileTraits<256, 1>::EPI_BYTES) {
+    *why = "fused RMSNorm keeps a row in shared memory: N is too large (limit about 53000)";
     return cudaErrorInvalidValue;
   }
   int grid = g.sm_count > 0 ? g.sm_count : device_sm_count();
   const int sms = device_sm_count();
   if (grid > sms) grid = sms;  // every CTA must be resident: CTAs wait on one another's output
-  if (!p.reduce && grid > p.TM * p.TN) grid = p.TM * p.TN;
+  if (!p.reduce && grid > p.TM * p.TN * tc.ctas) grid = p.TM * p.TN * tc.ctas;
+  if (tc.ctas == 2 && grid < 2) grid = 2;
   const bool bf16 = g.dtype == DT_BF16;
+  if (tc.ctas == 2) {
+    if (tc.bn == 256) {
+      return bf16 ? launch_instance<256, true, 2>(p, grid, stream) : launch_instance<256, false, 2>(p, grid, stream);
+    }
+    return bf16 ? launch_instance<128, true, 2>(p, grid, stream) : launch_instance<128, false, 2>(p, grid, stream);
+  }
   switch (tc.bn) {
     case 256:
-      return bf16 ? launch_instance<256, true>(p, grid, stream) : launch_instance<256, false>(p, grid, stream);
+      return bf16 ? launch_instance<256, true, 1>(p, grid, stream) : launch_instance<256, false, 1>(p, grid, stream);
     case 128:
-      return bf16 ? launch_instance<128, true>(p, grid, stream) : launch_instance<128, false>(p, grid, stream);
+      return bf16 ? launch_instance<128, true, 1>(p, grid, stream) : launch_instance<128, false, 1>(p, grid, stream);
     default:
-      return bf16 ? launch_instance<64, true>(p, grid, stream) : launch_instance<64, false>(p, grid, stream);
+      return bf16 ? launch_instance<64, true, 1>(p, grid, stream) : launch_instance<64, false, 1>(p, grid, stream);
   }
 }
 

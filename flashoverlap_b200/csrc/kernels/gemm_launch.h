@@ -11,13 +11,17 @@ enum DType : int { DT_F16 = 0, DT_BF16 = 1 };
 
 // Tile configurations selectable through the reference's `Algo` index
 // (reference: src/tiling/gemm_tiling.cuh:3-10 lists its six; these are the
-// tcgen05 shapes used here).  BM is always 128 (one UMMA M), BK always 64.
+// tcgen05 shapes used here).  BK is always 64.
+// ctas == 2: the tile is computed by a pair of CTAs (tcgen05.mma.cta_group::2),
+// 128 rows each.
 struct TileConfig {
   int bm, bn, bk;
+  int ctas;
 };
-constexpr int kNumAlgos = 3;
+constexpr int kNumAlgos = 5;
 inline TileConfig algo_config(int algo) {
-  static const TileConfig table[kNumAlgos] = {{128, 256, 64}, {128, 128, 64}, {128, 64, 64}};
+  static const TileConfig table[kNumAlgos] = {
+      {128, 256, 64, 1}, {128, 128, 64, 1}, {128, 64, 64, 1}, {256, 256, 64, 2}, {256, 128, 64, 2}};
   return table[(algo < 0 || algo >= kNumAlgos) ? 0 : algo];
 }
 

@@ -79,6 +79,7 @@ void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
   p.status = status_dev_;
   p.timeout_ns = timeout_ns_;
   p.raster_group = raster_group_;
+  p.phase_trace = phase_trace_;
   p.epi_layout.ld = 0;
 }
 
@@ -108,7 +109,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   GemmOperands g = g_in;
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
-  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_rmsnorm: too many tile rows");
+  if (g.M / 128 > kMaxTileRows) throw std::runtime_error("gemm_rmsnorm: too many tile rows");
   const int set = static_cast<int>(calls_ & 1ull);
   check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
   FusedParams p;
@@ -142,7 +143,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
   if (g.M % world_ != 0) throw std::runtime_error("gemm_allreduce: M must be divisible by the world size");
-  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_allreduce: too many tile rows");
+  if (g.M / 128 > kMaxTileRows) throw std::runtime_error("gemm_allreduce: too many tile rows");
   ensure_workspace(g.M, g.N);
   const int set = static_cast<int>(calls_ & 1ull);
   check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
@@ -190,9 +191,9 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
   if (g.M % world_ != 0) throw std::runtime_error("gemm_reducescatter: M must be divisible by the world size");
-  if (g.M / tc.bm > kMaxTileRows) throw std::runtime_error("gemm_reducescatter: too many tile rows");
+  if (g.M / 128 > kMaxTileRows) throw std::runtime_error("gemm_reducescatter: too many tile rows");
   const int rows_local = g.M / world_;
-  if (!interleave && world_ > 1 && rows_local % tc.bm != 0) {
+  if (!interleave && world_ > 1 && rows_local % 128 != 0) {
     throw std::runtime_error("gemm_reducescatter: contiguous ownership needs (M / world) % 128 == 0");
   }
   ensure_workspace(g.M, g.N);

@@ -55,6 +55,9 @@ class FusedEngine {
   void set_timeout_ms(long long ms) { timeout_ns_ = static_cast<unsigned long long>(ms) * 1000000ull; }
   void set_sm_count(int n) { sm_count_ = n; }
   void set_raster_group(int g) { raster_group_ = g; }
+  // Device buffer of 4 x uint64 per CTA that every following launch fills with
+  // its phase timestamps (null = off).
+  void set_phase_trace(unsigned long long* buf) { phase_trace_ = buf; }
 
   // C[M,N] = A[M,K] * B[N,K]^T on this GPU only.  `layout` null = row-major.
   void gemm(const GemmOperands& g, void* C, const OutLayout* layout, const SignalArgs* sig, cudaStream_t stream);
@@ -110,6 +113,7 @@ class FusedEngine {
   unsigned long long timeout_ns_ = 20000000000ull;
   int sm_count_ = 0;
   int raster_group_ = 0;  // 0 = choose per operation
+  unsigned long long* phase_trace_ = nullptr;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
 };
 

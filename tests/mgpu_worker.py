@@ -64,7 +64,9 @@ def main():
     for dtype in (torch.float16, torch.bfloat16):
         tol = 1e-2 if dtype == torch.float16 else 3e-2
         for i, (M, N, K) in enumerate(shapes):
-            for algo in (0, 1):
+            for algo in (0, 1, 3):
+                if algo == 3 and (M // world) % 256:
+                    continue
                 A, B, W = inputs(M, N, K, dtype, i)
                 ref = full_sum(A, B)
                 tag = f"{str(dtype)[6:]} M{M} N{N} K{K} algo{algo}"

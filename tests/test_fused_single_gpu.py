@@ -34,7 +34,7 @@ def make_inputs(M, N, K, dtype, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("algo", [0, 1, 2])
+@pytest.mark.parametrize("algo", [0, 1, 2, 3, 4])
 def test_gemm_rmsnorm_single_kernel(dtype, algo):
     M, N, K = 1024, 4096, 512
     A, B, W = make_inputs(M, N, K, dtype)
