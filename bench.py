@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--algo", type=int, default=0)
+    ap.add_argument("--algo", type=int, default=3, help="tile configuration (3 = 256x256 CTA pair)")
     ap.add_argument("--no-detail", action="store_true", help="skip the baseline and the second shape")
     return ap.parse_args()
 
@@ -60,7 +60,7 @@ def main():
     from flashoverlap_b200.models import FusedRowParallelLinear
     from flashoverlap_b200.parallel import init_distributed, make_baseline_impl, make_overlap_impl, max_over_ranks
     from flashoverlap_b200.utils.clocks import ClockSampler
-    from flashoverlap_b200.utils.timing import time_steps
+    from flashoverlap_b200.utils.timing import time_pairs, time_steps
 
     if not torch.cuda.is_available():
         print(json.dumps({"error": "bench.py needs a CUDA device"}))
@@ -134,15 +134,17 @@ def main():
             base.gemm_allreduce(x, layer.weight, C)
             torch.ops.flashoverlap_op.rmsnorm(C, O, layer.norm_weight, eps)
 
-        bt = time_steps(base_step, steps, warmup, flush=True)
+        # fused and baseline steps alternate so that both see the same clocks
+        ft, bt = time_pairs(step, base_step, steps, warmup)
+        fused_ms2 = max_over_ranks(sum(ft)) / steps
         base_ms = max_over_ranks(sum(bt)) / steps
-        gt = time_steps(lambda: impl.cutlass_gemm(x, layer.weight, C, args.algo), steps, warmup, flush=True)
+        gt, ct = time_pairs(lambda: impl.cutlass_gemm(x, layer.weight, C, args.algo),
+                            lambda: base.cublas_gemm(x, layer.weight, C), steps, warmup)
         gemm_ms = max_over_ranks(sum(gt)) / steps
-        ct = time_steps(lambda: base.cublas_gemm(x, layer.weight, C), steps, warmup, flush=True)
         cublas_ms = max_over_ranks(sum(ct)) / steps
         detail["ar_fp16"] = {
-            "fused_ms": round(ms_per_step, 4), "nccl_baseline_ms": round(base_ms, 4),
-            "speedup_vs_nccl_baseline": round(base_ms / ms_per_step, 3),
+            "fused_ms": round(fused_ms2, 4), "nccl_baseline_ms": round(base_ms, 4),
+            "speedup_vs_nccl_baseline": round(base_ms / fused_ms2, 3), "measured": "alternating steps",
             "own_gemm_ms": round(gemm_ms, 4), "cublas_gemm_ms": round(cublas_ms, 4),
         }
         # second shape: MLP down-projection, GEMM + ReduceScatter + RMSNorm, bf16
@@ -154,14 +156,13 @@ def main():
         D2 = torch.empty(M2 // world, N2, device=dev, dtype=torch.bfloat16)
         C2 = torch.empty(M2, N2, device=dev, dtype=torch.bfloat16)
         O2 = torch.empty_like(D2)
-        rt = time_steps(lambda: impl.gemm_reducescatter_fused(A2, B2, D2, W2, eps, args.algo, False), steps, warmup)
-        rs_ms = max_over_ranks(sum(rt)) / steps
-
         def base_rs():
             base.gemm_reducescatter(A2, B2, C2, D2)
             torch.ops.flashoverlap_op.rmsnorm(D2, O2, W2, eps)
 
-        brt = time_steps(base_rs, steps, warmup)
+        rt, brt = time_pairs(lambda: impl.gemm_reducescatter_fused(A2, B2, O2, W2, eps, args.algo, False), base_rs,
+                             steps, warmup)
+        rs_ms = max_over_ranks(sum(rt)) / steps
         base_rs_ms = max_over_ranks(sum(brt)) / steps
         detail["rs_bf16"] = {
             "M": M2, "N": N2, "K_per_rank": K2, "fused_ms": round(rs_ms, 4), "nccl_baseline_ms": round(base_rs_ms, 4),

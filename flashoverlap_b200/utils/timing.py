@@ -47,3 +47,33 @@ def time_steps(fn: Callable[[], None], steps: int, warmup: int, flush: bool = Tr
         dist.barrier(group)
         torch.cuda.synchronize()
     return [s.elapsed_time(e) for s, e in zip(starts, ends)]
+
+
+def time_pairs(fn_a: Callable[[], None], fn_b: Callable[[], None], steps: int, warmup: int, flush: bool = True,
+               group=None) -> tuple[list[float], list[float]]:
+    """Per-step device times of two alternatives measured in alternation
+    (a, b, a, b, ...) so that clock and power drift hit both alike."""
+    import torch.distributed as dist
+
+    for _ in range(warmup):
+        for fn in (fn_a, fn_b):
+            if flush:
+                flush_l2()
+            fn()
+    torch.cuda.synchronize()
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier(group)
+        torch.cuda.synchronize()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+    for i in range(steps):
+        for j, fn in enumerate((fn_a, fn_b)):
+            if flush:
+                flush_l2()
+            ev[i][2 * j].record()
+            fn()
+            ev[i][2 * j + 1].record()
+    torch.cuda.synchronize()
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier(group)
+        torch.cuda.synchronize()
+    return ([e[0].elapsed_time(e[1]) for e in ev], [e[2].elapsed_time(e[3]) for e in ev])
