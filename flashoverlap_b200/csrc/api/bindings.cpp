@@ -119,10 +119,15 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_rmsnorm", &OverlapImpl::GemmRmsNorm)
+      .def("attach_symmetric", &OverlapImpl::AttachSymmetric)
+      .def("set_use_nvls", &OverlapImpl::SetUseNvls)
+      .def("nvls_available", &OverlapImpl::NvlsAvailable)
+      .def("p2p_push", &OverlapImpl::P2pPush)
       .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)
       .def("set_phase_trace", &OverlapImpl::SetPhaseTrace)
+      .def("set_reduce_group", &OverlapImpl::SetReduceGroup)
       .def("status", &OverlapImpl::Status)
       .def("status_string", &OverlapImpl::StatusString)
       .def("check_status", &OverlapImpl::CheckStatus)

@@ -363,12 +363,33 @@ void OverlapImpl::GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tens
   engine_.gemm_rmsnorm(g, C.data_ptr(), O.data_ptr(), norm, current_stream());
 }
 
+void OverlapImpl::AttachSymmetric(std::vector<int64_t> peer_ptrs, int64_t mc_ptr, int64_t nbytes) {
+  TORCH_CHECK(engine_ready_, "attach_symmetric: call nccl_init first");
+  TORCH_CHECK(static_cast<int>(peer_ptrs.size()) == comm_.world(), "attach_symmetric: need one pointer per rank");
+  TORCH_CHECK(nbytes > 0, "attach_symmetric: nbytes must be positive");
+  std::vector<void*> ptrs;
+  for (int64_t v : peer_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(v)));
+  engine_.attach_symmetric(static_cast<size_t>(nbytes), ptrs, reinterpret_cast<void*>(static_cast<uintptr_t>(mc_ptr)));
+}
+void OverlapImpl::SetUseNvls(bool allreduce, bool reducescatter) { engine_.set_use_nvls(allreduce, reducescatter); }
+bool OverlapImpl::NvlsAvailable() { return engine_.nvls_available(); }
+
+void OverlapImpl::P2pPush(int64_t bytes, int64_t ctas) {
+  require_comm("p2p_push");
+  TORCH_CHECK(engine_ready_, "p2p_push: call nccl_init first");
+  engine_.p2p_push(bytes, static_cast<int>(ctas), current_stream());
+}
+
 void OverlapImpl::SetTimeoutMs(int64_t ms) {
   TORCH_CHECK(ms > 0, "timeout must be positive");
   engine_.set_timeout_ms(ms);
 }
 void OverlapImpl::SetSmCount(int64_t n) { engine_.set_sm_count(static_cast<int>(n)); }
 void OverlapImpl::SetRasterGroup(int64_t g) { engine_.set_raster_group(static_cast<int>(g)); }
+void OverlapImpl::SetReduceGroup(int64_t g) {
+  TORCH_CHECK(g == 0 || g == 1 || g == 2 || g == 4 || g == 8, "reduce group must be 0, 1, 2, 4 or 8");
+  engine_.set_reduce_group(static_cast<int>(g));
+}
 void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
   if (buf.numel() == 0) {
     engine_.set_phase_trace(nullptr);

@@ -53,10 +53,23 @@ class OverlapImpl : public torch::CustomClassHolder {
   void GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
                    int64_t algo);
 
+  // Collective.  Gives the object symmetric memory allocated elsewhere:
+  // `peer_ptrs[r]` is rank r's buffer mapped into this process, `mc_ptr` the
+  // multicast address (0 = none), `nbytes` the size of each buffer.  With a
+  // multicast address the fused operations reduce through NVLink SHARP.
+  void AttachSymmetric(std::vector<int64_t> peer_ptrs, int64_t mc_ptr, int64_t nbytes);
+  void SetUseNvls(bool allreduce, bool reducescatter);
+  bool NvlsAvailable();
+
+  // Collective: all-to-all push of `bytes` per peer with the P2P store kernel
+  // (bandwidth tool); `ctas` = 0 uses every SM.
+  void P2pPush(int64_t bytes, int64_t ctas);
+
   // ---- tuning knobs and failure reporting ---------------------------------
   void SetTimeoutMs(int64_t ms);
   void SetSmCount(int64_t n);
   void SetRasterGroup(int64_t g);
+  void SetReduceGroup(int64_t g);
   // Every following launch records per-CTA phase timestamps into `buf`
   // (int64, at least 4 * SM count entries; an empty tensor turns it off).
   void SetPhaseTrace(at::Tensor buf);

@@ -89,6 +89,7 @@ struct alignas(64) FusedParams {
 
   // ---- reduce phase ---------------------------------------------------------
   int reduce;                      // 0 = kernel ends after the GEMM
+  int reduce_group;                // warps that share one row in the reduce phase: 1, 2, 4 or 8
   const void* stage;               // this GPU's staging: [ws][rows_per_owner][N]
   uint32_t flag_target;            // value every arrival counter must reach
   int norm;                        // apply RMSNorm after the sum
@@ -99,6 +100,19 @@ struct alignas(64) FusedParams {
   OutLayout out_layout;
   uint32_t* done[kMaxRanks];       // per-rank "rows delivered" counter (all-reduce)
   uint32_t done_target;
+
+  // ---- NVLink SHARP mode -----------------------------------------------------
+  // nvls == 1: the epilogue keeps the partial tiles in this GPU's own staging
+  // buffer ([M][N], natural order, epi_base[0]); the owner of a row pulls the
+  // sum over all ranks with multimem.ld_reduce, and an all-reduce result is
+  // written to every rank with multimem.st.  The mc_* pointers are multicast
+  // addresses of the staging buffer, arrival counters, result buffer and
+  // delivery counter.
+  int nvls;
+  const void* mc_stage;
+  uint32_t* mc_flag;
+  void* mc_out;
+  uint32_t* mc_done;
 
   // ---- phase trace ----------------------------------------------------------
   // Optional: per CTA {kernel start, end of the GEMM phase, end of the reduce

@@ -7,11 +7,12 @@
 //   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma / tcgen05.commit)
 //   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end)
-//   warp 3      idle during the GEMM phase
+//   warp 3      signalling     (one lane publishes finished tiles at system scope
+//                               and bumps the owners' arrival counters)
 // With CTAS == 2 two such CTAs form a cluster: both stage operands and run an
 // epilogue for their own 128 rows, the MMA warp of rank 0 issues for the pair.
 //   warps 4-7   epilogue       (tcgen05.ld -> convert -> smem transpose ->
-//                               coalesced 16-byte stores -> arrival counter)
+//                               coalesced 16-byte stores)
 // After its last tile the whole CTA joins the reduce phase (one row per warp).
 //
 // Replaces, as one launch, the reference's signalling GEMM + wait kernel +
@@ -142,52 +143,66 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
 // of loads in flight.  WS > 0 fixes the number of ranks at compile time (all
 // loads of a batch are issued before the first use); WS == 0 is the generic
 // fallback for other group sizes.
-template <bool BF16, int WS>
-__device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem, int smem_bytes, int warp, int lane,
-                                             uint64_t deadline, volatile uint32_t* abort_flag) {
+template <bool BF16, int WS, bool NVLS>
+__device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem, int smem_bytes, float* red,
+                                             int warp, int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
   constexpr int BM = 128;
+  // NVLS: one load-reduce per chunk replaces the ws loads (instantiated with WS == 1)
   constexpr int U = WS == 0 ? 1 : (WS == 1 ? 8 : (WS == 2 ? 4 : 2));  // chunks per lane per batch
   constexpr int NS = WS == 0 ? kMaxRanks : WS;
-  const int ws = WS == 0 ? p.ws : WS;
+  constexpr int kWarps = kThreads / 32;
+  const int ws = NVLS ? p.ws : (WS == 0 ? p.ws : WS);
+  const int nsrc = NVLS ? 1 : ws;  // loads per chunk
   const int n_chunks = p.N >> 3;  // 16-byte chunks per row
   const int row_bytes = p.N * 2;
   const uint32_t smem_base = ptx::smem_u32(smem);
+  // G warps share one row (G = 1, 2, 4 or 8); few rows per CTA -> larger G
+  const int G = p.reduce_group;
+  int groups = kWarps / G;
+  const int gidx = warp / G;  // row group of this warp
+  const int wg = warp - gidx * G;
 
   // RMSNorm: the weight vector is staged in shared memory once per CTA, then
-  // one row buffer per active warp follows it.
-  int rows_per_iter = kThreads / 32;
+  // one row buffer per row group follows it.
   if (p.norm) {
     const uint16_t* gamma = reinterpret_cast<const uint16_t*>(p.gamma);
     for (int c = threadIdx.x; c < n_chunks; c += kThreads) {
       ptx::st_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4), *reinterpret_cast<const uint4*>(gamma + c * 8));
     }
     const int fit = (smem_bytes - row_bytes) / row_bytes;
-    if (fit < rows_per_iter) rows_per_iter = fit;
+    if (fit < groups) groups = fit;
     __syncthreads();
   }
-  if (rows_per_iter < 1 || warp >= rows_per_iter) return;  // (< 1 is rejected on the host)
+  if (groups < 1 || gidx >= groups) return;  // (< 1 is rejected on the host)
   const uint32_t gbuf = smem_base;
-  const uint32_t rowbuf = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(warp + 1);
+  const uint32_t rowbuf = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(gidx + 1);
   const int rows_local = p.rows_per_owner;
   const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
   const long long src_stride = static_cast<long long>(rows_local) * p.N;
   const uint32_t* my_flag = p.flag[p.me];
+  const int cl = wg * 32 + lane;  // first chunk of this lane
+  const int cstep = 32 * G;       // chunk stride between a lane's chunks
 
   auto load_batch = [&](uint4 (&v)[U][NS], const uint16_t* src0, int c0) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int c = c0 + 32 * u;
+      const int c = c0 + cstep * u;
       if (c < n_chunks) {
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
-          if (s < ws) v[u][s] = ptx::ld_cg_v4(src0 + s * src_stride + c * 8);
+          if (s < nsrc) {
+            if constexpr (NVLS) v[u][s] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
+            else v[u][s] = ptx::ld_cg_v4(src0 + s * src_stride + c * 8);
+          }
         }
       }
     }
   };
   auto store_out = [&](int out_row, int c, const uint4& o) {
     const long long off = layout_offset(p.out_layout, out_row, c * 8);
-    if (p.bcast) {
+    if (NVLS && p.bcast) {
+      ptx::multimem_st_v4(reinterpret_cast<uint16_t*>(p.mc_out) + off, o);  // lands on every rank
+    } else if (p.bcast) {
 #pragma unroll
       for (int r = 0; r < NS; ++r) {
         if (r < ws) {
@@ -202,7 +217,7 @@ __device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem
   };
 
   for (int i = 0;; ++i) {
-    const int lr = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (warp + rows_per_iter * i);
+    const int lr = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (gidx + groups * i);
     if (lr >= rows_local) break;
     int g;  // global row
     if (p.own_mode == OWN_BLOCK) g = p.me * rows_local + lr;
@@ -221,77 +236,97 @@ __device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem
       }
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok) break;
 
     const int out_row = p.bcast ? g : lr;
-    const uint16_t* src0 = stage + static_cast<long long>(lr) * p.N;
+    // NVLS: partials sit at their global row in every rank's staging buffer
+    const uint16_t* src0 = NVLS ? reinterpret_cast<const uint16_t*>(p.mc_stage) + static_cast<long long>(g) * p.N
+                                : stage + static_cast<long long>(lr) * p.N;
     float ssq = 0.f;
-    // software pipeline: the loads of batch k+1 are in flight while batch k is summed
-    uint4 cur[U][NS], nxt[U][NS];
-    load_batch(cur, src0, lane);
-    for (int c0 = lane; c0 < n_chunks; c0 += 32 * U) {
-      if (c0 + 32 * U < n_chunks) load_batch(nxt, src0, c0 + 32 * U);
+    if (ok) {
+      // software pipeline: the loads of batch k+1 are in flight while batch k is summed
+      uint4 cur[U][NS], nxt[U][NS];
+      load_batch(cur, src0, cl);
+      for (int c0 = cl; c0 < n_chunks; c0 += cstep * U) {
+        if (c0 + cstep * U < n_chunks) load_batch(nxt, src0, c0 + cstep * U);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int c = c0 + 32 * u;
-        if (c < n_chunks) {
-          float a[8];
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + cstep * u;
+          if (c < n_chunks) {
+            float a[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) a[e] = 0.f;
+            for (int e = 0; e < 8; ++e) a[e] = 0.f;
 #pragma unroll
-          for (int s = 0; s < NS; ++s) {
-            if (s < ws) {
+            for (int s = 0; s < NS; ++s) {
+              if (s < nsrc) {
+                float2 f;
+                f = unpack2<BF16>(cur[u][s].x); a[0] += f.x; a[1] += f.y;
+                f = unpack2<BF16>(cur[u][s].y); a[2] += f.x; a[3] += f.y;
+                f = unpack2<BF16>(cur[u][s].z); a[4] += f.x; a[5] += f.y;
+                f = unpack2<BF16>(cur[u][s].w); a[6] += f.x; a[7] += f.y;
+              }
+            }
+            uint4 h;
+            h.x = pack2<BF16>(a[0], a[1]);
+            h.y = pack2<BF16>(a[2], a[3]);
+            h.z = pack2<BF16>(a[4], a[5]);
+            h.w = pack2<BF16>(a[6], a[7]);
+            if (p.norm) {
               float2 f;
-              f = unpack2<BF16>(cur[u][s].x); a[0] += f.x; a[1] += f.y;
-              f = unpack2<BF16>(cur[u][s].y); a[2] += f.x; a[3] += f.y;
-              f = unpack2<BF16>(cur[u][s].z); a[4] += f.x; a[5] += f.y;
-              f = unpack2<BF16>(cur[u][s].w); a[6] += f.x; a[7] += f.y;
+              f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
+              f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
+              f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
+              f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
+              ptx::st_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4), h);
+            } else {
+              store_out(out_row, c, h);
             }
           }
-          uint4 h;
-          h.x = pack2<BF16>(a[0], a[1]);
-          h.y = pack2<BF16>(a[2], a[3]);
-          h.z = pack2<BF16>(a[4], a[5]);
-          h.w = pack2<BF16>(a[6], a[7]);
-          if (p.norm) {
-            float2 f;
-            f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
-            f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
-            f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
-            f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
-            ptx::st_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4), h);
-          } else {
-            store_out(out_row, c, h);
-          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
-        for (int s = 0; s < NS; ++s) cur[u][s] = nxt[u][s];
+          for (int s = 0; s < NS; ++s) cur[u][s] = nxt[u][s];
+        }
       }
     }
     if (p.norm) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-      const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
-      // each lane re-reads exactly the chunks it wrote, so no warp barrier is needed
+      if (G > 1) {
+        // combine the partial sums of the G warps of this row group; the slot
+        // alternates with the row so that a fast warp cannot overwrite a value
+        // a slow warp of the same group has yet to read
+        float* slot = red + (i & 1) * kWarps + gidx * G;
+        if (lane == 0) slot[wg] = ssq;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + gidx), "r"(G * 32) : "memory");
+        ssq = 0.f;
+        for (int w = 0; w < G; ++w) ssq += slot[w];
+      }
+      if (ok) {
+        const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
+        // each lane re-reads exactly the chunks it wrote, so no barrier is needed for the row buffer
 #pragma unroll 4
-      for (int c = lane; c < n_chunks; c += 32) {
-        const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
-        const uint4 w = ptx::ld_shared_v4(gbuf + (static_cast<uint32_t>(c) << 4));
-        float2 f;
-        uint4 o;
-        f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
-        f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
-        f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
-        f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
-        store_out(out_row, c, o);
+        for (int c = cl; c < n_chunks; c += cstep) {
+          const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
+          const uint4 w = ptx::ld_shared_v4(gbuf + (static_cast<uint32_t>(c) << 4));
+          float2 f;
+          uint4 o;
+          f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
+          f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
+          f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
+          f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
+          store_out(out_row, c, o);
+        }
       }
     }
+    if (!ok) continue;  // keep taking part in the group barriers of later rows; their waits fail at once
     if (p.bcast) {
-      __syncwarp();  // every lane's stores of this row precede the releases below
-      if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
+      __syncwarp();  // every lane's stores of this row part precede the releases below
+      if constexpr (NVLS) {
+        if (lane == 0) ptx::multimem_red_release_add(p.mc_done, 1u);
+      } else {
+        if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
+      }
     }
   }
 }
@@ -321,6 +356,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* epi_prog = tmem_slot + 4;  // [4] tiles finished by each epilogue warp
+  float* red = reinterpret_cast<float*>(bars + 40);  // [2][8] partial sums of the reduce phase
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -337,6 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       ptx::mbar_init(&tempty_bar[i], T::EPI_WARPS * CTAS);  // the leader hears from both epilogues
     }
     *abort_flag = 0;
+    for (int i = 0; i < 4; ++i) epi_prog[i] = 0;
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
   }
@@ -489,7 +527,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       ptx::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
       const int row0 = m_blk * TILE_M + static_cast<int>(cta_rank) * BM + q * 32;  // first global row of this warp's slab
-      const int flag_blk = row0 / BM;  // 128-row block the arrival counters are kept for
 
 #pragma unroll 1
       for (int cc = 0; cc < BN / 64; ++cc) {
@@ -535,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           const uint4 v = ptx::ld_shared_v4(slab + r * 128 + ((chunk ^ (r & 7)) << 4));
           const int g = row0 + r;
           uint16_t* dst;
-          if (p.own_mode == OWN_SINGLE) {
+          if (p.own_mode == OWN_SINGLE || p.nvls) {
             dst = reinterpret_cast<uint16_t*>(p.epi_base[0]) + layout_offset(p.epi_layout, g, col);
           } else if (p.own_mode == OWN_BLOCK) {
             const int o = g / p.rows_per_owner;
@@ -551,36 +588,73 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         __syncwarp();
       }
 
-      // ---- signalling: the slab is written; make it visible, then count ----
-      if (p.flag[0] != nullptr) {
-        // __syncwarp above ordered every lane's stores before this point; the
-        // release on the reduction publishes them at system scope.
-        if (p.own_mode == OWN_INTERLEAVE) {
-          if (lane < p.ws) ptx::red_release_sys_add(p.flag[lane] + flag_blk, 1u);
-        } else if (p.own_mode == OWN_BLOCK) {
-          if (lane == 0) ptx::red_release_sys_add(p.flag[row0 / p.rows_per_owner] + flag_blk, 1u);
-        } else {
-          if (lane == 0) ptx::red_release_sys_add(p.flag[0] + flag_blk, 1u);
-        }
-      }
-      if (q == 0 && lane == 0 && cta_rank == 0 && (p.seg_counter != nullptr || p.ticket_counter != nullptr)) {
-        // Reference-compatible bookkeeping, once per tile.  (The three other
-        // epilogue warps of this tile may still be storing; consumers of these
-        // counters run after the kernel, in stream order.)
-        const int tile_id = m_blk * p.TN + n_blk;
-        const int slot = p.slot_of_tile ? p.slot_of_tile[tile_id] : tile_id;
-        if (p.seg_counter != nullptr) {
-          int seg = 0, acc = 0;
-          for (; seg < p.nseg; ++seg) {
-            acc += p.cseg[seg];
-            if (slot < acc) break;
+      // ---- progress: this warp's slab of the tile is written ----
+      // (__syncwarp above ordered every lane's stores before this release; the
+      // signalling warp acquires it and publishes the tile at system scope, so
+      // that no epilogue warp ever waits for a system-scope fence.)
+      if (lane == 0) ptx::st_release_cta_shared(&epi_prog[q], static_cast<uint32_t>(it + 1));
+    }
+  } else if (warp == 3) {
+    // ===================== signalling =====================
+    // One thread per CTA follows the epilogue warps tile by tile: when all four
+    // have stored their slabs it fences at system scope and bumps the arrival
+    // counter of the tile's 128-row block on the GPU(s) that own those rows,
+    // and keeps the reference-compatible counters.
+    const bool wanted = p.flag[0] != nullptr || p.seg_counter != nullptr || p.ticket_counter != nullptr;
+    if (lane == 0 && wanted) {
+      int it = 0;
+      bool ok = true;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
+        const uint32_t need = static_cast<uint32_t>(it + 1);
+        uint32_t spins = 0;
+        while (true) {
+          uint32_t lo = ptx::ld_acquire_cta_shared(&epi_prog[0]);
+#pragma unroll
+          for (int w = 1; w < 4; ++w) {
+            const uint32_t v = ptx::ld_acquire_cta_shared(&epi_prog[w]);
+            lo = v < lo ? v : lo;
           }
-          if (seg < p.nseg) atomicAdd(p.seg_counter + seg, 1);
+          if (lo >= need) break;
+          if ((++spins & 0xffu) == 0u && (*abort_flag || ptx::globaltimer_ns() > deadline)) {
+            ok = false;  // the epilogue gave up (it has reported why) or ran out of time
+            break;
+          }
+          __nanosleep(32);
         }
-        if (p.ticket_counter != nullptr) {
-          const int ticket = atomicAdd(p.ticket_counter, 1);
-          if (slot >= 0 && slot < num_tiles) p.trace[slot] = ticket;
-          else report_error(p.status, ST_BAD_INDEX, p.me, 0x500u, slot, num_tiles);
+        if (!ok) break;
+        int m_blk, n_blk;
+        tile_coords(p, t, m_blk, n_blk);
+        const int blk_row0 = m_blk * TILE_M + static_cast<int>(cta_rank) * BM;
+        const int flag_blk = blk_row0 / BM;
+        if (p.flag[0] != nullptr) {
+          ptx::fence_acq_rel_sys();
+          if (p.nvls) {
+            ptx::multimem_red_relaxed_add(p.mc_flag + flag_blk, 1u);  // lands on every rank
+          } else if (p.own_mode == OWN_INTERLEAVE) {
+            for (int r = 0; r < p.ws; ++r) ptx::red_relaxed_sys_add(p.flag[r] + flag_blk, 1u);
+          } else if (p.own_mode == OWN_BLOCK) {
+            ptx::red_relaxed_sys_add(p.flag[blk_row0 / p.rows_per_owner] + flag_blk, 1u);
+          } else {
+            ptx::red_relaxed_sys_add(p.flag[0] + flag_blk, 1u);
+          }
+        }
+        if (cta_rank == 0 && (p.seg_counter != nullptr || p.ticket_counter != nullptr)) {
+          // Reference-compatible bookkeeping, once per tile.
+          const int tile_id = m_blk * p.TN + n_blk;
+          const int slot = p.slot_of_tile ? p.slot_of_tile[tile_id] : tile_id;
+          if (p.seg_counter != nullptr) {
+            int seg = 0, acc = 0;
+            for (; seg < p.nseg; ++seg) {
+              acc += p.cseg[seg];
+              if (slot < acc) break;
+            }
+            if (seg < p.nseg) atomicAdd(p.seg_counter + seg, 1);
+          }
+          if (p.ticket_counter != nullptr) {
+            const int ticket = atomicAdd(p.ticket_counter, 1);
+            if (slot >= 0 && slot < num_tiles) p.trace[slot] = ticket;
+            else report_error(p.status, ST_BAD_INDEX, p.me, 0x500u, slot, num_tiles);
+          }
         }
       }
     }
@@ -608,12 +682,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
 
   // ===================== reduce phase =====================
   ptx::fence_proxy_async_smem();  // the pipeline's shared memory is reused through the generic proxy
-  switch (p.ws) {
-    case 1: reduce_phase<BF16, 1>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
-    case 2: reduce_phase<BF16, 2>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
-    case 4: reduce_phase<BF16, 4>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
-    case 8: reduce_phase<BF16, 8>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
-    default: reduce_phase<BF16, 0>(p, smem, T::STAGES * T::STAGE_BYTES + T::EPI_BYTES, warp, lane, deadline, abort_flag); break;
+  constexpr int kRowSmem = T::STAGES * T::STAGE_BYTES + T::EPI_BYTES;
+  if (p.nvls) {
+    reduce_phase<BF16, 1, true>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag);
+  } else {
+    switch (p.ws) {
+      case 1: reduce_phase<BF16, 1, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
+      case 2: reduce_phase<BF16, 2, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
+      case 4: reduce_phase<BF16, 4, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
+      case 8: reduce_phase<BF16, 8, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
+      default: reduce_phase<BF16, 0, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
+    }
   }
 
   if (p.phase_trace != nullptr && lane == 0) {

@@ -129,6 +129,14 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
   int grid = g.sm_count > 0 ? g.sm_count : device_sm_count();
   const int sms = device_sm_count();
   if (grid > sms) grid = sms;  // every CTA must be resident: CTAs wait on one another's output
+  if (p.reduce) {
+    if (p.reduce_group != 1 && p.reduce_group != 2 && p.reduce_group != 4 && p.reduce_group != 8) {
+      // few rows per CTA: let several warps share a row so that every SM stays busy
+      const int per_cta = p.rows_per_owner / (grid > 0 ? grid : 1);
+      p.reduce_group = per_cta >= 16 ? 1 : (per_cta >= 8 ? 2 : (per_cta >= 4 ? 4 : 8));
+    }
+    if (p.bcast) p.done_target *= static_cast<uint32_t>(p.reduce_group);  // one delivery count per warp and row
+  }
   if (!p.reduce && grid > p.TM * p.TN * tc.ctas) grid = p.TM * p.TN * tc.ctas;
   if (tc.ctas == 2 && grid < 2) grid = 2;
   const bool bf16 = g.dtype == DT_BF16;

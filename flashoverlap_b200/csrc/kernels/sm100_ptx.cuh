@@ -267,6 +267,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void red_release_sys_add(uint32_t* addr, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t* addr, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+// CTA-scope release / acquire on a shared-memory word (progress counters
+// between warps of one CTA).
+__device__ __forceinline__ void st_release_cta_shared(uint32_t* smem_word, uint32_t v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(smem_word)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* smem_word) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(smem_word)) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
@@ -295,6 +308,40 @@ __device__ __forceinline__ bool wait_counter_geq(const uint32_t* addr, uint32_t 
     }
     __nanosleep(64);
   }
+}
+
+// ----------------------------------------------------------------------------
+// NVLink SHARP (multimem): one address of a multicast mapping stands for the
+// same offset in every GPU's memory.  A load-reduce returns the sum over all
+// GPUs (added in fp32 inside the switch, rounded once), a store or reduction
+// is applied on every GPU.
+// ----------------------------------------------------------------------------
+template <bool BF16>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_v4(const void* mc_ptr) {
+  uint4 v;
+  if constexpr (BF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_ptr)
+                 : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_ptr)
+                 : "memory");
+  }
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc_ptr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_red_relaxed_add(uint32_t* mc_ptr, uint32_t v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_release_add(uint32_t* mc_ptr, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
 }
 
 // 16-byte global accesses that bypass L1 (data written by peers or by other

@@ -40,9 +40,52 @@ uint32_t* FusedEngine::flag_ptr(int rank, int set) const {
 }
 uint32_t* FusedEngine::done_ptr(int rank, int set) const { return flag_ptr(rank, set) + kMaxTileRows; }
 
+namespace {
+size_t workspace_bytes(long long elems) {
+  const size_t mat = static_cast<size_t>(elems) * 2;
+  return 4 * (mat + 4096) + 2 * (kFlagWords * 4 + 4096) + 8192 + (1 << 20);
+}
+}  // namespace
+
+void FusedEngine::carve_workspace(long long elems) {
+  const size_t mat = static_cast<size_t>(elems) * 2;
+  heap_.reset_allocator();
+  for (int s = 0; s < 2; ++s) ws_.stage[s] = heap_.alloc(mat, 1024);
+  for (int s = 0; s < 2; ++s) ws_.result[s] = heap_.alloc(mat, 1024);
+  for (int s = 0; s < 2; ++s) ws_.flags[s] = heap_.alloc(kFlagWords * 4, 1024);
+  ws_.misc = heap_.alloc(4096, 1024);
+  ws_.capacity_elems = elems;
+  calls_ = 0;
+  pushes_ = 0;
+}
+
+void FusedEngine::attach_symmetric(size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr) {
+  if (!initialized()) throw std::runtime_error("attach_symmetric: engine not initialised");
+  if (heap_.valid()) {
+    check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    heap_.destroy();
+  }
+  heap_.attach(rank_, world_, bytes, peer_ptrs, mc_ptr);
+  check(cudaMemset(heap_.local(0), 0, bytes), "cudaMemset(symmetric memory)");
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  if (world_ > 1 && all_gather_) {  // nobody signals into memory that is not zeroed yet
+    char t = 1;
+    std::vector<char> all(world_);
+    all_gather_(&t, 1, all.data());
+  }
+  // the largest problem the attached memory can hold
+  long long elems = static_cast<long long>((bytes - workspace_bytes(0)) / 8);
+  if (elems < 1) throw std::runtime_error("attach_symmetric: buffer too small");
+  carve_workspace(elems);
+}
+
 void FusedEngine::ensure_workspace(long long m, long long n) {
   const long long elems = m * n;
   if (heap_.valid() && ws_.capacity_elems >= elems) return;
+  if (heap_.valid() && !heap_.owned()) {
+    throw std::runtime_error("the attached symmetric memory is too small for this problem: need " +
+                             std::to_string(workspace_bytes(elems)) + " bytes");
+  }
   if (heap_.valid()) {
     // Growing: all ranks get here in the same call.  Drain the device, then a
     // gather as a barrier so that no peer still writes into the old slab.
@@ -54,14 +97,8 @@ void FusedEngine::ensure_workspace(long long m, long long n) {
     }
     heap_.destroy();
   }
-  const size_t mat = static_cast<size_t>(elems) * 2;
-  const size_t total = 4 * (mat + 4096) + 2 * (kFlagWords * 4 + 4096) + (1 << 20);
-  heap_.init(rank_, world_, total, all_gather_);
-  for (int s = 0; s < 2; ++s) ws_.stage[s] = heap_.alloc(mat, 1024);
-  for (int s = 0; s < 2; ++s) ws_.result[s] = heap_.alloc(mat, 1024);
-  for (int s = 0; s < 2; ++s) ws_.flags[s] = heap_.alloc(kFlagWords * 4, 1024);
-  ws_.capacity_elems = elems;
-  calls_ = 0;
+  heap_.init(rank_, world_, workspace_bytes(elems), all_gather_);
+  carve_workspace(elems);
 }
 
 void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
@@ -79,6 +116,7 @@ void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
   p.status = status_dev_;
   p.timeout_ns = timeout_ns_;
   p.raster_group = raster_group_;
+  p.reduce_group = reduce_group_;
   p.phase_trace = phase_trace_;
   p.epi_layout.ld = 0;
 }
@@ -124,7 +162,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   if (p.raster_group == 0) p.raster_group = 4;
   p.reduce = 1;
   p.stage = scratch;
-  p.flag_target = static_cast<uint32_t>((g.N / tc.bn) * 4);
+  p.flag_target = static_cast<uint32_t>(g.N / tc.bn);
   p.norm = norm.gamma != nullptr;
   p.gamma = norm.gamma;
   p.eps = norm.eps;
@@ -162,10 +200,18 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
     p.done[r] = done_ptr(r, set);
   }
   p.epi_layout.ld = g.N;
+  if (use_nvls_ && nvls_available()) {
+    p.nvls = 1;
+    p.epi_base[0] = heap_.local(ws_.stage[set]);  // partials stay here, [M][N]
+    p.mc_stage = heap_.mc(ws_.stage[set]);
+    p.mc_flag = static_cast<uint32_t*>(heap_.mc(ws_.flags[set]));
+    p.mc_out = heap_.mc(ws_.result[set]);
+    p.mc_done = static_cast<uint32_t*>(heap_.mc(ws_.flags[set])) + kMaxTileRows;
+  }
   if (p.raster_group == 0) p.raster_group = 2;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
-  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn) * 4);
+  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
   p.norm = norm.gamma != nullptr;
   p.gamma = norm.gamma;
   p.eps = norm.eps;
@@ -210,6 +256,12 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
     p.flag[r] = flag_ptr(r, set);
   }
   p.epi_layout.ld = g.N;
+  if (use_nvls_rs_ && nvls_available()) {
+    p.nvls = 1;
+    p.epi_base[0] = heap_.local(ws_.stage[set]);
+    p.mc_stage = heap_.mc(ws_.stage[set]);
+    p.mc_flag = static_cast<uint32_t*>(heap_.mc(ws_.flags[set]));
+  }
   if (p.own_mode == OWN_BLOCK) {
     // start with the tile rows of the next rank so that at any moment the
     // ranks push to different owners
@@ -218,7 +270,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   if (p.raster_group == 0) p.raster_group = 2;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
-  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn) * 4);
+  p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
   p.norm = norm.gamma != nullptr;
   p.gamma = norm.gamma;
   p.eps = norm.eps;
@@ -229,6 +281,32 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   const char* why = nullptr;
   check_launch(launch_fused(g, p, stream, &why), why, "gemm_reducescatter");
   ++calls_;
+}
+
+void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("p2p_push: engine not initialised");
+  if (bytes <= 0 || bytes % 16 != 0) throw std::runtime_error("p2p_push: bytes must be a positive multiple of 16");
+  ensure_workspace(static_cast<long long>(world_) * bytes / 2 + 8, 1);
+  if (ctas <= 0) ctas = device_sm_count();
+  PushParams p{};
+  p.src = heap_.local(ws_.stage[0]);
+  p.bytes = bytes;
+  p.src_stride = 0;
+  p.ws = world_;
+  p.me = rank_;
+  p.include_self = 0;
+  for (int r = 0; r < world_; ++r) {
+    p.dst[r] = static_cast<char*>(heap_.ptr(r, ws_.result[0])) + static_cast<size_t>(rank_) * bytes;
+    p.flag[r] = static_cast<uint32_t*>(heap_.ptr(r, ws_.misc));
+  }
+  check(launch_p2p_push(p, ctas, stream), "p2p_push launch");
+  pushes_ += static_cast<unsigned long long>(world_ - 1) * ctas;  // arrivals expected here so far
+  if (world_ > 1) {
+    const uint32_t target = static_cast<uint32_t>(pushes_);
+    check(launch_wait_counter(static_cast<uint32_t*>(heap_.local(ws_.misc)), target, timeout_ns_, status_dev_, rank_,
+                              stream),
+          "wait_counter launch");
+  }
 }
 
 StatusWord FusedEngine::read_status() {
@@ -252,6 +330,7 @@ void FusedEngine::reset_counters() {
   }
   if (heap_.valid()) {
     for (int s = 0; s < 2; ++s) check(cudaMemset(flag_ptr(rank_, s), 0, kFlagWords * 4), "cudaMemset(counters)");
+    check(cudaMemset(heap_.local(ws_.misc), 0, 4096), "cudaMemset(counters)");
     check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
   }
   if (world_ > 1 && all_gather_) {
@@ -260,6 +339,7 @@ void FusedEngine::reset_counters() {
     all_gather_(&t, 1, all.data());
   }
   calls_ = 0;
+  pushes_ = 0;
   clear_status();
 }
 

@@ -18,8 +18,10 @@
 #include <cuda_runtime.h>
 
 #include <string>
+#include <vector>
 
 #include "../kernels/fused_params.h"
+#include "../kernels/comm_kernels.h"
 #include "../kernels/gemm_launch.h"
 #include "symm_heap.h"
 
@@ -55,6 +57,8 @@ class FusedEngine {
   void set_timeout_ms(long long ms) { timeout_ns_ = static_cast<unsigned long long>(ms) * 1000000ull; }
   void set_sm_count(int n) { sm_count_ = n; }
   void set_raster_group(int g) { raster_group_ = g; }
+  // Warps sharing one row in the reduce phase (1, 2, 4, 8; 0 = choose from the row count).
+  void set_reduce_group(int g) { reduce_group_ = g; }
   // Device buffer of 4 x uint64 per CTA that every following launch fills with
   // its phase timestamps (null = off).
   void set_phase_trace(unsigned long long* buf) { phase_trace_ = buf; }
@@ -82,6 +86,26 @@ class FusedEngine {
   void gemm_reducescatter(const GemmOperands& g, void* D, bool interleave, const NormArgs& norm,
                           const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream);
 
+  // Collective bandwidth primitive: every rank stores `bytes` to each of the
+  // other ranks with the push kernel and then waits, on the device, until the
+  // pushes of all peers have landed here.  Used by the bandwidth-curve tool.
+  void p2p_push(long long bytes, int ctas, cudaStream_t stream);
+
+  // Collective.  Hands the engine externally allocated symmetric memory (see
+  // SymmHeap::attach) to carve its workspace from; with a multicast mapping
+  // the fused operations switch to the NVLink SHARP path.  The memory is
+  // zero-filled here and must outlive the engine.
+  void attach_symmetric(size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr);
+  bool nvls_available() const { return heap_.valid() && heap_.has_multicast() && world_ > 1; }
+  // Which operations take the NVLink SHARP path when it is available.
+  // Default: all-reduce yes (it halves the inbound traffic), reduce-scatter no
+  // (pushing partial tiles while the GEMM runs hides the transfer, a pull
+  // after the GEMM cannot).
+  void set_use_nvls(bool allreduce, bool reducescatter) {
+    use_nvls_ = allreduce;
+    use_nvls_rs_ = reducescatter;
+  }
+
   // Collective.  Makes sure the symmetric workspace can hold an M x N problem.
   void ensure_workspace(long long m, long long n);
 
@@ -99,6 +123,7 @@ class FusedEngine {
     size_t stage[2] = {0, 0};
     size_t result[2] = {0, 0};
     size_t flags[2] = {0, 0};  // kMaxTileRows arrival counters + 1 delivery counter each
+    size_t misc = 0;           // counters that the per-call clearing must not touch
     long long capacity_elems = 0;
   };
   void base_params(FusedParams& p, const SignalArgs* sig);
@@ -113,8 +138,13 @@ class FusedEngine {
   unsigned long long timeout_ns_ = 20000000000ull;
   int sm_count_ = 0;
   int raster_group_ = 0;  // 0 = choose per operation
+  int reduce_group_ = 0;
+  bool use_nvls_ = true;
+  bool use_nvls_rs_ = false;
+  void carve_workspace(long long elems);
   unsigned long long* phase_trace_ = nullptr;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
+  unsigned long long pushes_ = 0;  // arrivals expected at the push counter so far
 };
 
 }  // namespace fo

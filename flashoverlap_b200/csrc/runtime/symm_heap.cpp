@@ -1,5 +1,6 @@
 #include "symm_heap.h"
 
+#include <cstdint>
 #include <cstring>
 #include <stdexcept>
 
@@ -54,8 +55,35 @@ void SymmHeap::init(int rank, int world, size_t bytes, const AllGatherFn& all_ga
   all_gather(&token, 1, tokens.data());
 }
 
+void SymmHeap::attach(int rank, int world, size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr) {
+  if (valid()) throw std::runtime_error("SymmHeap::attach: heap already initialised");
+  if (world < 1 || rank < 0 || rank >= world || static_cast<int>(peer_ptrs.size()) != world) {
+    throw std::runtime_error("SymmHeap::attach: bad rank / world / pointer list");
+  }
+  for (void* p : peer_ptrs) {
+    if (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 1023u)) {
+      throw std::runtime_error("SymmHeap::attach: peer pointers must be non-null and 1024-byte aligned");
+    }
+  }
+  rank_ = rank;
+  world_ = world;
+  bytes_ = bytes;
+  top_ = 0;
+  peer_base_ = peer_ptrs;
+  base_ = peer_ptrs[rank];
+  mc_base_ = mc_ptr;
+  owned_ = false;
+}
+
 void SymmHeap::destroy() {
   if (!valid()) return;
+  if (!owned_) {
+    peer_base_.clear();
+    base_ = mc_base_ = nullptr;
+    bytes_ = top_ = 0;
+    owned_ = true;
+    return;
+  }
   for (int r = 0; r < world_; ++r) {
     if (r != rank_ && peer_base_[r] != nullptr) cudaIpcCloseMemHandle(peer_base_[r]);
   }

@@ -35,6 +35,11 @@ class SymmHeap {
   // Collective.  Allocates `bytes` (rounded up to 2 MiB) on the current device,
   // zero-fills it and maps every peer's slab.
   void init(int rank, int world, size_t bytes, const AllGatherFn& all_gather);
+  // Adopts symmetric memory that somebody else allocated and mapped (for
+  // example torch.distributed._symmetric_memory): peer_ptrs[r] is rank r's slab
+  // as mapped into this process, mc_ptr the multicast (NVLink SHARP) mapping of
+  // all slabs or null.  The heap does not own the memory.
+  void attach(int rank, int world, size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr);
   // Unmaps peers and frees the slab.  The caller must make sure that no rank
   // still has kernels in flight that touch this heap.
   void destroy();
@@ -52,12 +57,18 @@ class SymmHeap {
 
   void* ptr(int rank, size_t offset) const { return static_cast<char*>(peer_base_[rank]) + offset; }
   void* local(size_t offset) const { return static_cast<char*>(base_) + offset; }
+  // Multicast address of `offset` (null when the heap has no multicast mapping).
+  void* mc(size_t offset) const { return mc_base_ ? static_cast<char*>(mc_base_) + offset : nullptr; }
+  bool has_multicast() const { return mc_base_ != nullptr; }
+  bool owned() const { return owned_; }
   bool contains_local(const void* p, size_t bytes) const;
 
  private:
   int rank_ = 0, world_ = 1;
   size_t bytes_ = 0, top_ = 0;
   void* base_ = nullptr;
+  void* mc_base_ = nullptr;
+  bool owned_ = true;
   std::vector<void*> peer_base_;
 };
 

@@ -1,5 +1,7 @@
 """Process-group bootstrap and construction of the communication objects."""
 from .bootstrap import (  # noqa: F401
+    attach_symmetric_memory,
+    workspace_bytes,
     broadcast_nccl_id,
     init_distributed,
     make_baseline_impl,

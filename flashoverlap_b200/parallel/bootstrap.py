@@ -70,13 +70,59 @@ def broadcast_nccl_id(group=None) -> list[int]:
     return [int(v) for v in t.cpu().tolist()]
 
 
-def make_overlap_impl(group=None, timeout_ms: Optional[int] = None):
-    """An initialised ``OverlapImpl`` for the ranks of ``group`` (collective)."""
+_symmetric_keepalive: list = []
+
+
+def attach_symmetric_memory(impl, nbytes: int, group=None) -> bool:
+    """Allocate ``nbytes`` of symmetric memory with
+    ``torch.distributed._symmetric_memory``, map it on all ranks of ``group``
+    and hand it to ``impl`` (collective).  When the mapping comes with an
+    NVLink SHARP multicast address the fused operations of ``impl`` use
+    ``multimem`` instructions.  Returns whether a multicast address exists."""
+    import torch.distributed._symmetric_memory as symm
+
+    grp = group if group is not None else dist.group.WORLD
+    dev = torch.device("cuda", torch.cuda.current_device())
+    buf = symm.empty(int(nbytes), dtype=torch.uint8, device=dev)
+    handle = symm.rendezvous(buf, grp)
+    off = int(getattr(handle, "offset", 0) or 0)  # position of `buf` inside the mapped block
+    mc = int(handle.multicast_ptr) + off if handle.multicast_ptr else 0
+    ptrs = [int(p) + off for p in handle.buffer_ptrs]
+    if ptrs[dist.get_rank(grp)] != buf.data_ptr():
+        raise RuntimeError("symmetric memory handle does not describe the allocated tensor")
+    impl.attach_symmetric(ptrs, mc, int(nbytes))
+    _symmetric_keepalive.append((buf, handle))  # the engine holds raw pointers into this memory
+    return mc != 0
+
+
+def workspace_bytes(max_m: int, max_n: int) -> int:
+    """Symmetric memory the engine needs for problems up to ``max_m x max_n``
+    (two staging and two result buffers of 16-bit values plus counters)."""
+    return 8 * max_m * max_n + (4 << 20)
+
+
+def make_overlap_impl(group=None, timeout_ms: Optional[int] = None, nvls: Optional[bool] = None,
+                      max_m: int = 8192, max_n: int = 8192):
+    """An initialised ``OverlapImpl`` for the ranks of ``group`` (collective).
+
+    ``nvls`` (default: the ``FLASHOVERLAP_NVLS`` environment variable, else on)
+    asks for symmetric memory with an NVLink SHARP multicast mapping sized for
+    problems up to ``max_m x max_n``; without it, or when the mapping cannot be
+    made, the object allocates peer-mapped memory itself on first use and its
+    fused operations move data with peer-to-peer stores."""
     rank, world = _world(group)
     impl = torch.classes.flashoverlap_class.OverlapImpl()
     impl.nccl_init(rank, world, broadcast_nccl_id(group))
     impl.cutlass_init()
     impl.overlap_init()
+    if nvls is None:
+        nvls = os.environ.get("FLASHOVERLAP_NVLS", "1") not in ("0", "false", "off")
+    if nvls and world > 1 and torch.cuda.is_available() and dist.get_backend(group) == "nccl":
+        try:
+            attach_symmetric_memory(impl, workspace_bytes(max_m, max_n), group)
+        except Exception as exc:  # fall back to the object's own peer-mapped heap
+            if rank == 0:
+                print(f"flashoverlap_b200: symmetric memory with multicast unavailable ({exc!r}); using P2P stores")
     env = os.environ.get("FLASHOVERLAP_TIMEOUT_MS")
     if timeout_ms is None and env:
         timeout_ms = int(env)

@@ -26,7 +26,9 @@ def rms_ref(x, w, eps):
 def main():
     rank, world, _ = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
-    impl = make_overlap_impl(timeout_ms=4000)
+    impl = make_overlap_impl(timeout_ms=4000, max_m=4096, max_n=4096)
+    if rank == 0:
+        print(f"mode: {'NVLS multimem' if impl.nvls_available() else 'P2P stores'}", flush=True)
     failures = 0
 
     def check(name, got, want, tol):

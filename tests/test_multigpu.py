@@ -21,15 +21,19 @@ def _world():
 
 
 @pytest.mark.timeout(900)
-def test_fused_ops_match_torch_semantics_on_all_gpus():
+@pytest.mark.parametrize("nvls", ["1", "0"], ids=["nvls", "p2p"])
+def test_fused_ops_match_torch_semantics_on_all_gpus(nvls):
     world = _world()
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     env = dict(os.environ)
     env.setdefault("MASTER_ADDR", "127.0.0.1")
+    env["FLASHOVERLAP_NVLS"] = nvls
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "mgpu_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=850)
     tail = "\n".join((res.stdout + "\n" + res.stderr).splitlines()[-60:])
     assert res.returncode == 0, tail
     assert "DONE failures=0" in res.stdout, tail
+    if nvls == "0":
+        assert "mode: P2P stores" in res.stdout, tail
