@@ -131,9 +131,12 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
   if (grid > sms) grid = sms;  // every CTA must be resident: CTAs wait on one another's output
   if (p.reduce) {
     if (p.reduce_group != 1 && p.reduce_group != 2 && p.reduce_group != 4 && p.reduce_group != 8) {
-      // few rows per CTA: let several warps share a row so that every SM stays busy
-      const int per_cta = p.rows_per_owner / (grid > 0 ? grid : 1);
-      p.reduce_group = per_cta >= 16 ? 1 : (per_cta >= 8 ? 2 : (per_cta >= 4 ? 4 : 8));
+      // Rows are latency-bound, so as many as possible should be in flight:
+      // take the widest row group that still covers all owned rows in one
+      // round (8 / G rows per CTA at a time).
+      int gsel = 8;
+      while (gsel > 1 && static_cast<long long>(grid) * (8 / gsel) < p.rows_per_owner) gsel >>= 1;
+      p.reduce_group = gsel;
     }
     if (p.bcast) p.done_target *= static_cast<uint32_t>(p.reduce_group);  // one delivery count per warp and row
   }

@@ -105,18 +105,20 @@ def make_overlap_impl(group=None, timeout_ms: Optional[int] = None, nvls: Option
                       max_m: int = 8192, max_n: int = 8192):
     """An initialised ``OverlapImpl`` for the ranks of ``group`` (collective).
 
-    ``nvls`` (default: the ``FLASHOVERLAP_NVLS`` environment variable, else on)
+    ``nvls`` (default: the ``FLASHOVERLAP_NVLS`` environment variable, else off)
     asks for symmetric memory with an NVLink SHARP multicast mapping sized for
-    problems up to ``max_m x max_n``; without it, or when the mapping cannot be
-    made, the object allocates peer-mapped memory itself on first use and its
-    fused operations move data with peer-to-peer stores."""
+    problems up to ``max_m x max_n``; the fused all-reduce then reduces with
+    ``multimem`` instructions.  Without it, or when the mapping cannot be made,
+    the object allocates peer-mapped memory itself on first use and its fused
+    operations move data with peer-to-peer stores (measured equally fast on
+    8 B200s, and independent of multicast support)."""
     rank, world = _world(group)
     impl = torch.classes.flashoverlap_class.OverlapImpl()
     impl.nccl_init(rank, world, broadcast_nccl_id(group))
     impl.cutlass_init()
     impl.overlap_init()
     if nvls is None:
-        nvls = os.environ.get("FLASHOVERLAP_NVLS", "1") not in ("0", "false", "off")
+        nvls = os.environ.get("FLASHOVERLAP_NVLS", "0") in ("1", "true", "on")
     if nvls and world > 1 and torch.cuda.is_available() and dist.get_backend(group) == "nccl":
         try:
             attach_symmetric_memory(impl, workspace_bytes(max_m, max_n), group)
