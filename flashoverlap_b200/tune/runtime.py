@@ -1,0 +1,169 @@
+"""GPU-side building blocks of the tuner and of the benchmark scripts: timing
+loops in the reference's style (CUDA events, warm-up, mean, MAX over ranks;
+reference: test/test.py:157-164,205-207), GEMM tile profiling, completion-order
+sampling and the timed run of one fused configuration."""
+from __future__ import annotations
+
+import os
+import sys
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import make_overlap_impl, max_over_ranks
+from ..utils.config import ALGO_TILES
+from ..utils.reorder import generate_row_mapping, reorder_indices
+from ..utils.timing import flush_l2
+from .model import div_up, hint_from_samples
+
+
+def dbg(msg: str) -> None:
+    """Debug line on stderr when FLASH_DEBUG is set (reference: tune/search.py:16-20)."""
+    if os.getenv("FLASH_DEBUG"):
+        print(f"[rank={os.getenv('LOCAL_RANK', '?')}] {msg}", flush=True, file=sys.stderr)
+
+
+def world() -> Tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def mean_time_ms(fn: Callable[[], None], warmup: int = 20, reps: int = 200, flush: bool = False) -> float:
+    """Mean device time of ``fn`` in ms, maximum over the ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+    for i in range(reps):
+        if flush:
+            flush_l2()
+        starts[i].record()
+        fn()
+        ends[i].record()
+    torch.cuda.synchronize()
+    local = sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / reps
+    return max_over_ranks(local)
+
+
+def make_inputs(M: int, N: int, K: int, dtype=torch.float16, std: float = 0.5):
+    A = torch.empty((M, K), dtype=dtype, device="cuda").normal_(mean=0.0, std=std)
+    B = torch.empty((N, K), dtype=dtype, device="cuda").normal_(mean=0.0, std=std)
+    C = torch.empty((M, N), dtype=dtype, device="cuda")
+    return A, B, C
+
+
+def usable_algos(M: int, N: int) -> List[int]:
+    return [i for i, (bm, bn, _) in enumerate(ALGO_TILES) if M % bm == 0 and N % bn == 0]
+
+
+def profile_gemm(impl, M: int, N: int, K: int, dtype=torch.float16, warmup: int = 10, reps: int = 100,
+                 keep: int = 10) -> Tuple[List[int], List[int], List[float], List[int]]:
+    """Times every tile configuration that fits the shape and returns the
+    ``keep`` fastest as stage-1 lists (reference: tune/profile_config.py:18-74)."""
+    A, B, C = make_inputs(M, N, K, dtype)
+    rows = []
+    for algo in usable_algos(M, N):
+        ms = mean_time_ms(lambda: impl.cutlass_gemm(A, B, C, algo), warmup, reps)
+        rows.append((ms, algo))
+        dbg(f"profile_gemm: algo {algo} {ALGO_TILES[algo]} {ms:.4f} ms")
+    if not rows:
+        raise ValueError(f"no tile configuration divides M={M}, N={N}")
+    rows.sort()
+    rows = rows[:keep]
+    return ([ALGO_TILES[a][0] for _, a in rows], [ALGO_TILES[a][1] for _, a in rows], [ms for ms, _ in rows],
+            [a for _, a in rows])
+
+
+def compute_hint(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, wave_size: int, comm_op: str,
+                 dtype=torch.float16, warmup: int = 20, samples: int = 20) -> Tuple[bool, List[int]]:
+    """Measured tile completion order -> tile-order hint (reference:
+    tune/search.py:131-291).  Runs the fused operation in monitor mode with the
+    identity order, collects the completion ticket of every tile ``samples``
+    times and votes.  Collective; the result of rank 0 is used by all ranks."""
+    rank, ws = world()
+    tm, tn = div_up(M, BM), div_up(N, BN)
+    tiles = tm * tn
+    waves = div_up(tiles, wave_size)
+    cseg = [min(wave_size, tiles - i * wave_size) for i in range(waves)]
+    if tn <= len(cseg):
+        # the monitor keeps its ticket counter in MM[N/BN - 1]: fold the groups
+        cseg = [tiles]
+    cseg_cpu = torch.tensor(cseg, dtype=torch.int32)
+    cseg_gpu = cseg_cpu.cuda()
+    A, B, C = make_inputs(M, N, K, dtype)
+    MM = torch.zeros((tm + 1, tn), dtype=torch.int32, device="cuda")
+    RA = torch.arange(tiles, dtype=torch.int32, device="cuda").reshape(tm, tn)
+    D = RE = None
+    if comm_op == "reduce_scatter":
+        D = torch.empty((M // ws, N), dtype=dtype, device="cuda")
+        RE = generate_row_mapping(M, N, BM, BN, cseg, ws, device="cuda")
+
+    def run(monitor: bool):
+        if comm_op == "all_reduce":
+            impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, monitor)
+        else:
+            impl.gemm_reducescatter_overlap(A, B, C, D, MM, RA, RE, 1, cseg_cpu, cseg_gpu, algo, monitor)
+
+    ok, hint = False, []
+    try:
+        for _ in range(warmup):
+            run(True)
+        torch.cuda.synchronize()
+        got = torch.empty((samples, tiles), dtype=torch.int32, device="cuda")
+        for i in range(samples):
+            MM[0] = 0
+            run(True)
+            got[i] = MM[1:].reshape(-1)
+        torch.cuda.synchronize()
+        impl.check_status()
+        ok, hint = hint_from_samples(got.cpu(), wave_size)
+    except RuntimeError as exc:
+        dbg(f"compute_hint: sampling failed: {exc}")
+    if ws > 1:
+        flag = torch.tensor([int(ok), len(hint)], dtype=torch.int64, device="cuda")
+        dist.broadcast(flag, src=0)
+        ok = bool(flag[0].item())
+        if ok:
+            h = torch.tensor(hint if rank == 0 else [0] * int(flag[1].item()), dtype=torch.int64, device="cuda")
+            dist.broadcast(h, src=0)
+            hint = h.cpu().tolist()
+        dist.barrier()
+    return ok, hint
+
+
+def perf_running(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, cseg: Sequence[int],
+                 hint: Sequence[int], comm_op: str, dtype=torch.float16, warmup: int = 20, reps: int = 200,
+                 raster_group: int = 0, reduce_group: int = 0) -> float:
+    """Mean time (ms, MAX over ranks) of the overlapped operation for one
+    solution; a single group means "no overlap": GEMM, then one collective
+    (reference: tune/search.py:357-459)."""
+    _, ws = world()
+    tm, tn = div_up(M, BM), div_up(N, BN)
+    tiles = tm * tn
+    cseg_cpu = torch.tensor(list(cseg), dtype=torch.int32)
+    cseg_gpu = cseg_cpu.cuda()
+    A, B, C = make_inputs(M, N, K, dtype)
+    MM = torch.zeros((max(tn, len(cseg)),), dtype=torch.int32, device="cuda")
+    RA = reorder_indices(tiles, hint, device="cuda").reshape(tm, tn)
+    D = torch.empty((M // ws, N), dtype=dtype, device="cuda") if comm_op == "reduce_scatter" else None
+    RE = generate_row_mapping(M, N, BM, BN, list(cseg), ws, device="cuda") if comm_op == "reduce_scatter" else None
+    impl.set_raster_group(raster_group)
+    impl.set_reduce_group(reduce_group)
+    if len(cseg) == 1:
+        if comm_op == "all_reduce":
+            fn = lambda: impl.gemm_allreduce(A, B, C, algo)  # noqa: E731
+        else:
+            fn = lambda: impl.gemm_reducescatter(A, B, C, D, algo)  # noqa: E731
+    elif comm_op == "all_reduce":
+        fn = lambda: impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, False)  # noqa: E731
+    else:
+        fn = lambda: impl.gemm_reducescatter_overlap(A, B, C, D, MM, RA, RE, 1, cseg_cpu, cseg_gpu, algo,  # noqa: E731
+                                                     False)
+    ms = mean_time_ms(fn, warmup, reps)
+    impl.check_status()
+    impl.set_raster_group(0)
+    impl.set_reduce_group(0)
+    return ms
