@@ -123,6 +123,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)
       .def("p2p_push", &OverlapImpl::P2pPush)
+      .def("wait_on_unset_counter", &OverlapImpl::WaitOnUnsetCounter)
       .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)

@@ -380,6 +380,11 @@ void OverlapImpl::P2pPush(int64_t bytes, int64_t ctas) {
   engine_.p2p_push(bytes, static_cast<int>(ctas), current_stream());
 }
 
+void OverlapImpl::WaitOnUnsetCounter(int64_t timeout_ms) {
+  TORCH_CHECK(timeout_ms > 0 && timeout_ms <= 5000, "timeout must be in (0, 5000] ms");
+  engine_.wait_on_unset_counter(timeout_ms, current_stream());
+}
+
 void OverlapImpl::SetTimeoutMs(int64_t ms) {
   TORCH_CHECK(ms > 0, "timeout must be positive");
   engine_.set_timeout_ms(ms);

@@ -66,6 +66,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   void P2pPush(int64_t bytes, int64_t ctas);
 
   // ---- tuning knobs and failure reporting ---------------------------------
+  // Failure-path self test, see FusedEngine::wait_on_unset_counter.
+  void WaitOnUnsetCounter(int64_t timeout_ms);
   void SetTimeoutMs(int64_t ms);
   void SetSmCount(int64_t n);
   void SetRasterGroup(int64_t g);

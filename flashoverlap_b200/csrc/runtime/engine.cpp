@@ -309,6 +309,17 @@ void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {
   }
 }
 
+void FusedEngine::wait_on_unset_counter(long long timeout_ms, cudaStream_t stream) {
+  if (!initialized()) init(0, 1, nullptr);
+  if (world_ == 1) ensure_workspace(1, 1);
+  if (!heap_.valid()) throw std::runtime_error("wait_on_unset_counter: no workspace yet");
+  // word 512 of the private counter page is never written by any kernel
+  const uint32_t* never = static_cast<uint32_t*>(heap_.local(ws_.misc)) + 512;
+  check(launch_wait_counter(never, 1u, static_cast<unsigned long long>(timeout_ms) * 1000000ull, status_dev_, rank_,
+                            stream),
+        "wait_counter launch");
+}
+
 StatusWord FusedEngine::read_status() {
   StatusWord s{};
   if (status_dev_ == nullptr) return s;

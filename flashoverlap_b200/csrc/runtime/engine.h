@@ -106,6 +106,11 @@ class FusedEngine {
     use_nvls_rs_ = reducescatter;
   }
 
+  // Failure-path self test: launches the bounded counter wait on a counter that
+  // nothing increments, with its own short deadline.  The wait must give up,
+  // record ST_TIMEOUT_FLAG in the status word and leave the context usable.
+  void wait_on_unset_counter(long long timeout_ms, cudaStream_t stream);
+
   // Collective.  Makes sure the symmetric workspace can hold an M x N problem.
   void ensure_workspace(long long m, long long n);
 

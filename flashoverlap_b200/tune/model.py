@@ -55,7 +55,7 @@ def comm_latency_ms(curve: torch.Tensor, elements: float, world_size: int, comm_
     if world_size <= 1 or elements <= 0:
         return 0.0
     curve = torch.as_tensor(curve, dtype=torch.float64)
-    xs, ys = curve[:, 0], curve[:, 1]
+    xs, ys = curve[:, 0].contiguous(), curve[:, 1].contiguous()
     x = float(elements)
     if x <= float(xs[0]):
         bw = float(ys[0])
