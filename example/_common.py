@@ -1,5 +1,15 @@
+"""Start-up shared with the tuning tools (tune/_common.py), loaded by path."""
+import importlib.util
 import os
-import sys
 
-sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tune"))
-from _common import DTYPES, finish, make_baseline_impl, make_overlap_impl, start, torch  # noqa: F401,E402
+_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tune", "_common.py")
+_spec = importlib.util.spec_from_file_location("_fo_tune_common", _path)
+_mod = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_mod)
+
+DTYPES = _mod.DTYPES
+finish = _mod.finish
+start = _mod.start
+make_baseline_impl = _mod.make_baseline_impl
+make_overlap_impl = _mod.make_overlap_impl
+torch = _mod.torch

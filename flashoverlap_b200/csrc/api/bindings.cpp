@@ -119,6 +119,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_rmsnorm", &OverlapImpl::GemmRmsNorm)
+      .def("allgather_gemm", &OverlapImpl::AllGatherGemm)
       .def("attach_symmetric", &OverlapImpl::AttachSymmetric)
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)

@@ -347,6 +347,23 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
   engine_.gemm_reducescatter(g, D.data_ptr(), interleave, norm, nullptr, nullptr, current_stream());
 }
 
+void OverlapImpl::AllGatherGemm(at::Tensor A_shard, at::Tensor B, at::Tensor C, int64_t algo) {
+  check_gemm_args(A_shard, B, nullptr);
+  require_comm("allgather_gemm");
+  TORCH_CHECK(engine_ready_, "allgather_gemm: call nccl_init first");
+  TORCH_CHECK(algo >= 0 && algo < kNumAlgos, "Algo out of range");
+  c10::cuda::CUDAGuard guard(A_shard.device());
+  const int ws = comm_.world();
+  const int64_t M = A_shard.size(0) * ws, N = B.size(0), K = A_shard.size(1);
+  const TileConfig tc = algo_config(static_cast<int>(algo));
+  TORCH_CHECK(M % tc.bm == 0 && N % tc.bn == 0 && K % 8 == 0, "need M % ", tc.bm, " == 0, N % ", tc.bn,
+              " == 0, K % 8 == 0 (M = ", M, ", N = ", N, ", K = ", K, ")");
+  check_matrix(C, "C");
+  TORCH_CHECK(C.scalar_type() == A_shard.scalar_type() && C.size(0) == M && C.size(1) == N, "C must be [M, N]");
+  engine_.allgather_gemm(A_shard.data_ptr(), B.data_ptr(), C.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+                         static_cast<int>(K), dtype_of(A_shard), static_cast<int>(algo), current_stream());
+}
+
 void OverlapImpl::GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
                               int64_t algo) {
   check_gemm_args(A, B, &C);

@@ -49,6 +49,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // GEMM + reduce-scatter (+ RMSNorm) into D [M/size, N].
   void GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor D, c10::optional<at::Tensor> weight, double eps,
                               int64_t algo, bool interleave);
+  // All-gather + GEMM in one launch: A_shard is this rank's [M/size, K] rows,
+  // C receives gather(A)[M, K] * B[N, K]^T.
+  void AllGatherGemm(at::Tensor A_shard, at::Tensor B, at::Tensor C, int64_t algo);
   // GEMM + RMSNorm on one GPU: C receives A*B^T, O the normalised rows.
   void GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
                    int64_t algo);

@@ -64,6 +64,7 @@ struct alignas(64) FusedParams {
   int M, N, K;
   int TM, TN;        // tile grid (BM = 128)
   int raster_group;  // tile rows walked column-major together (L2 reuse of B)
+  int force_full_grid;  // launch the requested number of CTAs even when there are fewer tiles
   int rot;           // first tile row (rotates ranks apart in block-ownership mode)
 
   // ---- GEMM epilogue destination -------------------------------------------
@@ -86,6 +87,12 @@ struct alignas(64) FusedParams {
   const uint32_t* a_ready;  // per source-rank counter; null = A is ready at launch
   uint32_t a_ready_target;
   int a_rows_per_rank;      // rows of A contributed by each rank
+  // All-gather push (done by warp 2 of every CTA while the GEMM starts on this
+  // rank's own shard): this rank's shard goes to every rank's gathered A.
+  const void* ag_src;            // this rank's shard [a_rows_per_rank, K]; null = no push
+  long long ag_bytes;            // bytes of one shard (multiple of 16)
+  void* ag_dst[kMaxRanks];       // where this rank's shard lives in rank r's gathered A
+  uint32_t* ag_flag[kMaxRanks];  // rank r's a_ready counter for this rank
 
   // ---- reduce phase ---------------------------------------------------------
   int reduce;                      // 0 = kernel ends after the GEMM

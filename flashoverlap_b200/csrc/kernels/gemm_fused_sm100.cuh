@@ -503,6 +503,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         }
       }
     }
+  } else if (warp == 2) {
+    // ===================== all-gather push =====================
+    // This rank's shard of A goes to every rank's gathered A, destination by
+    // destination: first its own copy (the GEMM starts there), then rank me-1
+    // (which works on this shard right after its own), me-2, ...  Warp 2 of every CTA takes an
+    // interleaved share; when a destination's share is written the warp fences
+    // at system scope and bumps that rank's shard counter.
+    if (p.ag_src != nullptr) {
+      const long long chunks = p.ag_bytes >> 4;
+      const long long stride = static_cast<long long>(gridDim.x) * 32;
+      const long long first = static_cast<long long>(blockIdx.x) * 32 + lane;
+      const char* src = static_cast<const char*>(p.ag_src);
+      for (int j = 0; j < p.ws; ++j) {
+        int d = p.me - j;
+        if (d < 0) d += p.ws;
+        char* dst = static_cast<char*>(p.ag_dst[d]);
+        long long c = first;
+        for (; c + 7 * stride < chunks; c += 8 * stride) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(src + ((c + u * stride) << 4));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) ptx::st_v4(dst + ((c + u * stride) << 4), v[u]);
+        }
+        for (; c < chunks; c += stride) {
+          ptx::st_v4(dst + (c << 4), *reinterpret_cast<const uint4*>(src + (c << 4)));
+        }
+        __syncwarp();
+        if (lane == 0) {
+          ptx::fence_acq_rel_sys();
+          ptx::red_relaxed_sys_add(p.ag_flag[d], 1u);
+        }
+      }
+    }
   } else if (warp >= 4) {
     // ===================== epilogue =====================
     const int q = warp & 3;  // TMEM lane quarter this warp may access

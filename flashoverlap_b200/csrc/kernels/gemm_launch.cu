@@ -140,7 +140,7 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
     }
     if (p.bcast) p.done_target *= static_cast<uint32_t>(p.reduce_group);  // one delivery count per warp and row
   }
-  if (!p.reduce && grid > p.TM * p.TN * tc.ctas) grid = p.TM * p.TN * tc.ctas;
+  if (!p.reduce && !p.force_full_grid && grid > p.TM * p.TN * tc.ctas) grid = p.TM * p.TN * tc.ctas;
   if (tc.ctas == 2 && grid < 2) grid = 2;
   const bool bf16 = g.dtype == DT_BF16;
   if (tc.ctas == 2) {

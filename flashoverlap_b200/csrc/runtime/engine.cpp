@@ -283,6 +283,61 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   ++calls_;
 }
 
+void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype,
+                                 int algo, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("allgather_gemm: engine not initialised");
+  const TileConfig tc = algo_config(algo);
+  if (M % world_ != 0) throw std::runtime_error("allgather_gemm: M must be divisible by the world size");
+  const int rows = M / world_;
+  if (rows % 128 != 0) throw std::runtime_error("allgather_gemm: M / world must be a multiple of 128");
+  if ((static_cast<long long>(rows) * K * 2) % 16 != 0) throw std::runtime_error("allgather_gemm: K must be a multiple of 8");
+  const long long need = static_cast<long long>(M) * (K > N ? K : N);
+  ensure_workspace(need, 1);
+  const int set = static_cast<int>(calls_ & 1ull);
+  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  FusedParams p;
+  base_params(p, nullptr);
+  GemmOperands g{};
+  g.A = heap_.local(ws_.stage[set]);  // the gathered A of this call
+  g.B = B;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.dtype = dtype;
+  g.algo = algo;
+  g.sm_count = sm_count_;
+  p.own_mode = OWN_SINGLE;
+  p.ws = world_;
+  p.me = rank_;
+  p.rows_per_owner = M;
+  p.epi_base[0] = C;
+  p.epi_layout.ld = N;
+  if (p.raster_group == 0) p.raster_group = 2;
+  // own shard first, then the shards in the order they are pushed to this rank
+  p.rot = (rank_ * rows) / tc.bm;
+  const size_t shard_bytes = static_cast<size_t>(rows) * K * 2;
+  uint32_t* ready = flag_ptr(rank_, set) + kMaxTileRows + 8;
+  p.a_ready = ready;
+  p.a_rows_per_rank = rows;
+  p.ag_src = A_shard;
+  p.ag_bytes = static_cast<long long>(shard_bytes);
+  for (int r = 0; r < world_; ++r) {
+    p.ag_dst[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + shard_bytes * rank_;
+    p.ag_flag[r] = flag_ptr(r, set) + kMaxTileRows + 8 + rank_;
+  }
+  const char* why = nullptr;
+  // every CTA pushes a share and bumps the counter once per destination
+  int grid = sm_count_ > 0 ? sm_count_ : device_sm_count();
+  if (grid > device_sm_count()) grid = device_sm_count();
+  if (tc.ctas == 2) grid &= ~1;
+  g.sm_count = grid;
+  p.a_ready_target = static_cast<uint32_t>(grid);
+  p.reduce = 0;
+  p.force_full_grid = 1;
+  check_launch(launch_fused(g, p, stream, &why), why, "allgather_gemm");
+  ++calls_;
+}
+
 void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {
   if (!initialized()) throw std::runtime_error("p2p_push: engine not initialised");
   if (bytes <= 0 || bytes % 16 != 0) throw std::runtime_error("p2p_push: bytes must be a positive multiple of 16");

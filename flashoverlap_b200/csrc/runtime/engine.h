@@ -86,6 +86,14 @@ class FusedEngine {
   void gemm_reducescatter(const GemmOperands& g, void* D, bool interleave, const NormArgs& norm,
                           const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream);
 
+  // Fused all-gather + GEMM (column-parallel linear on sequence-sharded
+  // activations): C[M, N] = gather_r(A_r)[M, K] * B[N, K]^T where every rank
+  // holds A_r = rows [r*M/world, (r+1)*M/world).  One launch: spare warps push
+  // this rank's shard to all ranks while the tensor cores start on it; tiles of
+  // other shards wait (bounded) for that shard's counter.  Collective.
+  void allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype, int algo,
+                      cudaStream_t stream);
+
   // Collective bandwidth primitive: every rank stores `bytes` to each of the
   // other ranks with the push kernel and then waits, on the device, until the
   // pushes of all peers have landed here.  Used by the bandwidth-curve tool.

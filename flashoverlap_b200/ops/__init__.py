@@ -1,5 +1,6 @@
 """Functional wrappers over the native operators."""
 from .functional import (  # noqa: F401
+    allgather_gemm,
     gemm,
     gemm_allreduce,
     gemm_reducescatter,

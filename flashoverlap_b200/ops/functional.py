@@ -47,6 +47,16 @@ def gemm_reducescatter(impl, a, b, world_size: int, norm_weight: Optional[torch.
     return out
 
 
+def allgather_gemm(impl, a_shard, b, world_size: int, algo: int = 0, out: Optional[torch.Tensor] = None):
+    """Fused all-gather + GEMM: ``gather(a_shard)[M, K] @ b[N, K]^T`` with the
+    gather pushed over NVLink by the same kernel that computes the product."""
+    _check(a_shard)
+    if out is None:
+        out = torch.empty((a_shard.size(0) * world_size, b.size(0)), dtype=a_shard.dtype, device=a_shard.device)
+    impl.allgather_gemm(a_shard, b, out, algo)
+    return out
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     _check(x)
     out = torch.empty_like(x)

@@ -96,6 +96,22 @@ def main():
                 torch.cuda.synchronize()
                 check(f"gemm+RS(interleave)+norm {tag}", D, rms_ref(ref[rank::world], W, 1e-5), tol)
 
+    # all-gather -> GEMM: every rank contributes M/world rows of A, computes all M rows of the product
+    for dtype in (torch.float16, torch.bfloat16):
+        for algo in (0, 3):
+            M, N, K = 256 * world, 512, 384
+            g = torch.Generator(device="cpu").manual_seed(4242)
+            A_full = torch.randn(M, K, generator=g).to(dev, dtype)
+            g2 = torch.Generator(device="cpu").manual_seed(5000 + rank)
+            Bn = (torch.randn(N, K, generator=g2) / K ** 0.5).to(dev, dtype)
+            rows = M // world
+            C = torch.full((M, N), float("nan"), device=dev, dtype=dtype)
+            for rep in range(3):  # repeated calls alternate the gathered-A buffers
+                impl.allgather_gemm(A_full[rank * rows:(rank + 1) * rows].contiguous(), Bn, C, algo)
+            torch.cuda.synchronize()
+            check(f"allgather+gemm {str(dtype)[6:]} algo{algo}", C, A_full.float() @ Bn.float().t(),
+                  1e-2 if dtype == torch.float16 else 3e-2)
+
     # back-to-back calls without host synchronisation (exercises both buffer sets)
     A, B, W = inputs(1024, 2048, 512, torch.float16, 9)
     ref = full_sum(A, B)

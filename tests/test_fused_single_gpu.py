@@ -144,3 +144,16 @@ def test_reorder_rmsnorm_rldn2():
         torch.cuda.synchronize()
         want = rms_ref(x, w, 1e-5)
         assert (o.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item(), f"rldn={rldn}"
+
+
+def test_allgather_gemm_world1():
+    M, N, K = 512, 1024, 256
+    A, B, _ = make_inputs(M, N, K, torch.bfloat16, seed=8)
+    impl = make_impl()
+    C = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    for algo in (0, 3):
+        impl.allgather_gemm(A, B, C, algo)
+        torch.cuda.synchronize()
+        impl.check_status()
+        ref = A.float() @ B.float().t()
+        assert (C.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item()
