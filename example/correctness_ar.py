@@ -2,7 +2,8 @@
 RMSNorm against matmul + dist.all_reduce + a PyTorch RMSNorm (reference:
 example/correctness_ar.py:99-127; tolerance 1e-2), plus the natively fused layer.
 
-    torchrun --nproc_per_node=2 example/correctness_ar.py --m 4096 --n 8192 --k 4096
+    torchrun --nproc_per_node=2 example/correctness_ar.py --m_dim 4096 --n_dim 8192 --k_dim 4096
+(under torchrun spell the options --m_dim/--n_dim/--k_dim: torchrun itself claims the prefix --m)
 """
 import argparse
 
@@ -25,9 +26,9 @@ def default_config(M, N):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=4096)
-    ap.add_argument("--n", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--m", "--m_dim", dest="m", type=int, default=4096)
+    ap.add_argument("--n", "--n_dim", dest="n", type=int, default=8192)
+    ap.add_argument("--k", "--k_dim", dest="k", type=int, default=4096)
     ap.add_argument("--path", default=None)
     args = ap.parse_args()
     rank, ws = start()

@@ -3,7 +3,8 @@ example/correctness_rs.py:100-142; tolerance 5e-2, prints the worst element).
 The overlapped layer keeps the rows ``r, r + size, ...`` on rank r, so the golden
 path feeds the same rows grouped by ``row % size`` to reduce_scatter_tensor.
 
-    torchrun --nproc_per_node=2 example/correctness_rs.py --m 4096 --n 8192 --k 4096
+    torchrun --nproc_per_node=2 example/correctness_rs.py --m_dim 4096 --n_dim 8192 --k_dim 4096
+(under torchrun spell the options --m_dim/--n_dim/--k_dim: torchrun itself claims the prefix --m)
 """
 import argparse
 
@@ -20,9 +21,9 @@ from flashoverlap_b200.utils.reorder import reorder_rows_by_world_size
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=4096)
-    ap.add_argument("--n", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--m", "--m_dim", dest="m", type=int, default=4096)
+    ap.add_argument("--n", "--n_dim", dest="n", type=int, default=8192)
+    ap.add_argument("--k", "--k_dim", dest="k", type=int, default=4096)
     ap.add_argument("--path", default=None)
     args = ap.parse_args()
     rank, ws = start()
