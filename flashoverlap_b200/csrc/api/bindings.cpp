@@ -120,6 +120,8 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_rmsnorm", &OverlapImpl::GemmRmsNorm)
       .def("allgather_gemm", &OverlapImpl::AllGatherGemm)
+      .def("a2a_dispatch_gemm", &OverlapImpl::A2aDispatchGemm)
+      .def("a2a_padded_rows", &OverlapImpl::A2aPaddedRows)
       .def("attach_symmetric", &OverlapImpl::AttachSymmetric)
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)

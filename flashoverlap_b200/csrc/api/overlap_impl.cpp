@@ -364,6 +364,38 @@ void OverlapImpl::AllGatherGemm(at::Tensor A_shard, at::Tensor B, at::Tensor C, 
                          static_cast<int>(K), dtype_of(A_shard), static_cast<int>(algo), current_stream());
 }
 
+int64_t OverlapImpl::A2aPaddedRows(at::Tensor mLen_CPU, int64_t algo) {
+  check_int_tensor(mLen_CPU, "mLen_CPU", false);
+  const int ws = comm_.world();
+  TORCH_CHECK(mLen_CPU.numel() == static_cast<int64_t>(ws) * ws, "mLen_CPU must be [size, size]");
+  TORCH_CHECK(algo >= 0 && algo < kNumAlgos, "Algo out of range");
+  return engine_.a2a_padded_rows(mLen_CPU.data_ptr<int>(), static_cast<int>(algo));
+}
+
+void OverlapImpl::A2aDispatchGemm(at::Tensor A_send, at::Tensor B, at::Tensor C, at::Tensor mLen_CPU, int64_t algo) {
+  check_gemm_args(A_send, B, nullptr);
+  require_comm("a2a_dispatch_gemm");
+  TORCH_CHECK(engine_ready_, "a2a_dispatch_gemm: call nccl_init first");
+  const int ws = comm_.world(), rank = comm_.rank();
+  const int64_t m_pad = A2aPaddedRows(mLen_CPU, algo);
+  const int* len = mLen_CPU.data_ptr<int>();
+  int64_t send = 0;
+  for (int j = 0; j < ws; ++j) {
+    TORCH_CHECK(len[rank * ws + j] >= 0, "mLen_CPU entries must be >= 0");
+    send += len[rank * ws + j];
+  }
+  TORCH_CHECK(A_send.size(0) >= send, "A_send has ", A_send.size(0), " rows but mLen_CPU sends ", send);
+  const int64_t N = B.size(0), K = A_send.size(1);
+  const TileConfig tc = algo_config(static_cast<int>(algo));
+  TORCH_CHECK(N % tc.bn == 0 && K % 8 == 0, "need N % ", tc.bn, " == 0 and K % 8 == 0");
+  check_matrix(C, "C");
+  TORCH_CHECK(C.scalar_type() == A_send.scalar_type() && C.size(0) >= m_pad && C.size(1) == N,
+              "C must be [>= ", m_pad, ", N]");
+  c10::cuda::CUDAGuard guard(A_send.device());
+  engine_.a2a_gemm(A_send.data_ptr(), B.data_ptr(), C.data_ptr(), len, static_cast<int>(N), static_cast<int>(K),
+                   dtype_of(A_send), static_cast<int>(algo), current_stream());
+}
+
 void OverlapImpl::GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
                               int64_t algo) {
   check_gemm_args(A, B, &C);

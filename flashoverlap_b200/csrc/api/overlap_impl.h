@@ -52,6 +52,11 @@ class OverlapImpl : public torch::CustomClassHolder {
   // All-gather + GEMM in one launch: A_shard is this rank's [M/size, K] rows,
   // C receives gather(A)[M, K] * B[N, K]^T.
   void AllGatherGemm(at::Tensor A_shard, at::Tensor B, at::Tensor C, int64_t algo);
+  // All-to-all dispatch + GEMM in one launch (see FusedEngine::a2a_gemm):
+  // A_send holds the rows for rank 0, 1, ... back to back, mLen_CPU[i][j] rows
+  // go from rank i to rank j, C needs a2a_padded_rows(mLen_CPU, algo) rows.
+  void A2aDispatchGemm(at::Tensor A_send, at::Tensor B, at::Tensor C, at::Tensor mLen_CPU, int64_t algo);
+  int64_t A2aPaddedRows(at::Tensor mLen_CPU, int64_t algo);
   // GEMM + RMSNorm on one GPU: C receives A*B^T, O the normalised rows.
   void GemmRmsNorm(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor O, at::Tensor weight, double eps,
                    int64_t algo);

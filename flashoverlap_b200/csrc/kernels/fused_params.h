@@ -86,11 +86,14 @@ struct alignas(64) FusedParams {
   // ---- A operand readiness (all-gather -> GEMM) -----------------------------
   const uint32_t* a_ready;  // per source-rank counter; null = A is ready at launch
   uint32_t a_ready_target;
-  int a_rows_per_rank;      // rows of A contributed by each rank
+  int a_src_end[kMaxRanks]; // source r contributed the rows [a_src_end[r-1], a_src_end[r]) of the gathered A
   // All-gather push (done by warp 2 of every CTA while the GEMM starts on this
   // rank's own shard): this rank's shard goes to every rank's gathered A.
-  const void* ag_src;            // this rank's shard [a_rows_per_rank, K]; null = no push
-  long long ag_bytes;            // bytes of one shard (multiple of 16)
+  // (all-gather: the same shard to everybody; all-to-all dispatch: a different
+  // block of rows, possibly empty, to every rank).
+  int ag_push;                          // 0 = no push
+  const void* ag_src[kMaxRanks];        // rows this rank sends to rank r
+  long long ag_bytes[kMaxRanks];        // their size in bytes (multiple of 16, may be 0)
   void* ag_dst[kMaxRanks];       // where this rank's shard lives in rank r's gathered A
   uint32_t* ag_flag[kMaxRanks];  // rank r's a_ready counter for this rank
 

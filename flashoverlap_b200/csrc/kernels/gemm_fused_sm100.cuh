@@ -412,17 +412,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         const int a_row = m_blk * TILE_M + static_cast<int>(cta_rank) * BM;
         const int b_row = n_blk * BN + static_cast<int>(cta_rank) * T::B_ROWS;
         if (p.a_ready != nullptr) {
-          // All-gathered A: rows of this tile come from one source rank; wait
-          // until that shard has landed in local memory, then order the
-          // generic-proxy arrival before the async-proxy (TMA) reads.
-          const int src = a_row / p.a_rows_per_rank;
-          uint32_t seen = 0;
-          if (!ptx::wait_counter_geq(p.a_ready + src, p.a_ready_target, deadline, &seen)) {
-            report_error(p.status, ST_TIMEOUT_GATHER, p.me, src, seen, p.a_ready_target);
-            *abort_flag = 1;
-            ok = false;
-            break;
+          // Gathered A: wait until every source rank whose rows overlap
+          // [a_row, a_row + BM) has delivered them into local memory, then order
+          // those generic-proxy writes before the async-proxy (TMA) reads.
+          for (int r = 0; r < p.ws && ok; ++r) {
+            const int r_begin = r == 0 ? 0 : p.a_src_end[r - 1];
+            const int r_end = p.a_src_end[r];
+            if (r_end <= r_begin || r_end <= a_row || r_begin >= a_row + BM) continue;
+            uint32_t seen = 0;
+            if (!ptx::wait_counter_geq(p.a_ready + r, p.a_ready_target, deadline, &seen)) {
+              report_error(p.status, ST_TIMEOUT_GATHER, p.me, r, seen, p.a_ready_target);
+              *abort_flag = 1;
+              ok = false;
+            }
           }
+          if (!ok) break;
           ptx::fence_proxy_async_all();
         }
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -445,6 +449,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
+          }
+        }
+      }
+      if (ok && p.a_ready != nullptr && blockIdx.x == 0) {
+        // The kernel may only end when every rank's pushes of this call have
+        // arrived, also those of ranks that sent this rank no rows: it keeps a
+        // rank from running more than one call ahead of a peer, which is what
+        // makes two alternating buffer and counter sets sufficient.
+        for (int r = 0; r < p.ws; ++r) {
+          uint32_t seen = 0;
+          if (!ptx::wait_counter_geq(p.a_ready + r, p.a_ready_target, deadline, &seen)) {
+            report_error(p.status, ST_TIMEOUT_GATHER, p.me, 0x100u + r, seen, p.a_ready_target);
+            break;
           }
         }
       }
@@ -510,14 +527,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     // (which works on this shard right after its own), me-2, ...  Warp 2 of every CTA takes an
     // interleaved share; when a destination's share is written the warp fences
     // at system scope and bumps that rank's shard counter.
-    if (p.ag_src != nullptr) {
-      const long long chunks = p.ag_bytes >> 4;
+    if (p.ag_push) {
       const long long stride = static_cast<long long>(gridDim.x) * 32;
       const long long first = static_cast<long long>(blockIdx.x) * 32 + lane;
-      const char* src = static_cast<const char*>(p.ag_src);
       for (int j = 0; j < p.ws; ++j) {
         int d = p.me - j;
         if (d < 0) d += p.ws;
+        const long long chunks = p.ag_bytes[d] >> 4;
+        const char* src = static_cast<const char*>(p.ag_src[d]);
         char* dst = static_cast<char*>(p.ag_dst[d]);
         long long c = first;
         for (; c + 7 * stride < chunks; c += 8 * stride) {

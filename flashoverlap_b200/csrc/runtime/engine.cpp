@@ -283,16 +283,15 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   ++calls_;
 }
 
-void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype,
-                                 int algo, cudaStream_t stream) {
-  if (!initialized()) throw std::runtime_error("allgather_gemm: engine not initialised");
+// Common part of all-gather -> GEMM and all-to-all dispatch -> GEMM.
+// src_for[r] / bytes_for[r]: what this rank sends to rank r; src_end[r]: end row
+// of source r's block in this rank's gathered buffer; M: rows of the
+// gathered buffer that take part in the GEMM (multiple of the tile height);
+// first_row: where this rank's own block starts (the GEMM begins there).
+void FusedEngine::gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M,
+                                int first_row, const void* B, void* C, int N, int K, DType dtype, int algo,
+                                const char* op, cudaStream_t stream) {
   const TileConfig tc = algo_config(algo);
-  if (M % world_ != 0) throw std::runtime_error("allgather_gemm: M must be divisible by the world size");
-  const int rows = M / world_;
-  if (rows % 128 != 0) throw std::runtime_error("allgather_gemm: M / world must be a multiple of 128");
-  if ((static_cast<long long>(rows) * K * 2) % 16 != 0) throw std::runtime_error("allgather_gemm: K must be a multiple of 8");
-  const long long need = static_cast<long long>(M) * (K > N ? K : N);
-  ensure_workspace(need, 1);
   const int set = static_cast<int>(calls_ & 1ull);
   check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
   FusedParams p;
@@ -305,7 +304,6 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
   g.K = K;
   g.dtype = dtype;
   g.algo = algo;
-  g.sm_count = sm_count_;
   p.own_mode = OWN_SINGLE;
   p.ws = world_;
   p.me = rank_;
@@ -313,19 +311,15 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
   p.epi_base[0] = C;
   p.epi_layout.ld = N;
   if (p.raster_group == 0) p.raster_group = 2;
-  // own shard first, then the shards in the order they are pushed to this rank
-  p.rot = (rank_ * rows) / tc.bm;
-  const size_t shard_bytes = static_cast<size_t>(rows) * K * 2;
-  uint32_t* ready = flag_ptr(rank_, set) + kMaxTileRows + 8;
-  p.a_ready = ready;
-  p.a_rows_per_rank = rows;
-  p.ag_src = A_shard;
-  p.ag_bytes = static_cast<long long>(shard_bytes);
+  p.rot = first_row / tc.bm;  // own rows first, then the blocks in the order they are pushed to this rank
+  p.a_ready = flag_ptr(rank_, set) + kMaxTileRows + 8;
+  p.ag_push = 1;
   for (int r = 0; r < world_; ++r) {
-    p.ag_dst[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + shard_bytes * rank_;
+    p.a_src_end[r] = src_end[r];
+    p.ag_src[r] = src_for[r];
+    p.ag_bytes[r] = bytes_for[r];
     p.ag_flag[r] = flag_ptr(r, set) + kMaxTileRows + 8 + rank_;
   }
-  const char* why = nullptr;
   // every CTA pushes a share and bumps the counter once per destination
   int grid = sm_count_ > 0 ? sm_count_ : device_sm_count();
   if (grid > device_sm_count()) grid = device_sm_count();
@@ -334,8 +328,81 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
   p.a_ready_target = static_cast<uint32_t>(grid);
   p.reduce = 0;
   p.force_full_grid = 1;
-  check_launch(launch_fused(g, p, stream, &why), why, "allgather_gemm");
+  // ag_dst is filled by the callers' layout: where my block lives on rank r
+  for (int r = 0; r < world_; ++r) p.ag_dst[r] = ag_dst_scratch_[r];
+  const char* why = nullptr;
+  check_launch(launch_fused(g, p, stream, &why), why, op);
   ++calls_;
+}
+
+void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype,
+                                 int algo, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("allgather_gemm: engine not initialised");
+  if (M % world_ != 0) throw std::runtime_error("allgather_gemm: M must be divisible by the world size");
+  const int rows = M / world_;
+  if (rows % 128 != 0) throw std::runtime_error("allgather_gemm: M / world must be a multiple of 128");
+  if (K % 8 != 0) throw std::runtime_error("allgather_gemm: K must be a multiple of 8");
+  ensure_workspace(static_cast<long long>(M) * (K > N ? K : N), 1);
+  const int set = static_cast<int>(calls_ & 1ull);
+  const size_t shard_bytes = static_cast<size_t>(rows) * K * 2;
+  const void* src_for[kMaxRanks];
+  long long bytes_for[kMaxRanks];
+  int src_end[kMaxRanks];
+  for (int r = 0; r < world_; ++r) {
+    src_for[r] = A_shard;
+    bytes_for[r] = static_cast<long long>(shard_bytes);
+    src_end[r] = (r + 1) * rows;
+    ag_dst_scratch_[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + shard_bytes * rank_;
+  }
+  gathered_gemm(src_for, bytes_for, src_end, M, rank_ * rows, B, C, N, K, dtype, algo, "allgather_gemm", stream);
+}
+
+int FusedEngine::a2a_padded_rows(const int* mlen, int algo) const {
+  const TileConfig tc = algo_config(algo);
+  int most = 0;
+  for (int j = 0; j < world_; ++j) {
+    int recv = 0;
+    for (int i = 0; i < world_; ++i) recv += mlen[i * world_ + j];
+    if (recv > most) most = recv;
+  }
+  if (most == 0) most = 1;
+  return (most + tc.bm - 1) / tc.bm * tc.bm;
+}
+
+void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int* mlen, int N, int K, DType dtype,
+                           int algo, cudaStream_t stream) {
+  if (!initialized()) throw std::runtime_error("a2a_gemm: engine not initialised");
+  if (K % 8 != 0) throw std::runtime_error("a2a_gemm: K must be a multiple of 8");
+  for (int i = 0; i < world_ * world_; ++i) {
+    if (mlen[i] < 0) throw std::runtime_error("a2a_gemm: negative row count");
+  }
+  const int m_pad = a2a_padded_rows(mlen, algo);  // the same on every rank
+  ensure_workspace(static_cast<long long>(m_pad) * (K > N ? K : N), 1);
+  const int set = static_cast<int>(calls_ & 1ull);
+  const size_t row_bytes = static_cast<size_t>(K) * 2;
+  const void* src_for[kMaxRanks];
+  long long bytes_for[kMaxRanks];
+  int src_end[kMaxRanks];
+  size_t send_off = 0;
+  int first_row = 0;
+  for (int r = 0; r < world_; ++r) {
+    // what I send to r, and where it lands there: behind the rows of the sources before me
+    src_for[r] = static_cast<const char*>(A_send) + send_off;
+    bytes_for[r] = static_cast<long long>(mlen[rank_ * world_ + r]) * static_cast<long long>(row_bytes);
+    send_off += static_cast<size_t>(bytes_for[r]);
+    size_t before = 0;
+    for (int i = 0; i < rank_; ++i) before += static_cast<size_t>(mlen[i * world_ + r]);
+    ag_dst_scratch_[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + before * row_bytes;
+  }
+  int acc = 0;
+  for (int i = 0; i < world_; ++i) {
+    if (i == rank_) first_row = acc;
+    acc += mlen[i * world_ + rank_];
+    src_end[i] = acc;
+  }
+  // Rows between `acc` and the padded height belong to nobody: the GEMM reads
+  // whatever an earlier call left there and writes scratch rows of C.
+  gathered_gemm(src_for, bytes_for, src_end, m_pad, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream);
 }
 
 void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {

@@ -94,6 +94,20 @@ class FusedEngine {
   void allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype, int algo,
                       cudaStream_t stream);
 
+  // Fused all-to-all dispatch + GEMM (tokens routed to the rank that holds
+  // their expert): rank i sends rows_to[j] = mlen[i*world + j] rows of A_send
+  // (packed in destination order, its own block included) to rank j; every rank
+  // then multiplies the rows it received (in source order) by its B:
+  // C[0 .. received) = recv[received, K] * B[N, K]^T.  C must have room for
+  // `padded_rows(mlen)` rows (the largest receive count over all ranks, rounded
+  // up to the tile height); rows past `received` are scratch.  One launch,
+  // same mechanism as allgather_gemm.  Collective; `mlen` is the full world x
+  // world matrix and must be identical on all ranks.
+  void a2a_gemm(const void* A_send, const void* B, void* C, const int* mlen, int N, int K, DType dtype, int algo,
+                cudaStream_t stream);
+  // Rows of the gathered buffer / of C needed by a2a_gemm for this matrix and Algo.
+  int a2a_padded_rows(const int* mlen, int algo) const;
+
   // Collective bandwidth primitive: every rank stores `bytes` to each of the
   // other ranks with the push kernel and then waits, on the device, until the
   // pushes of all peers have landed here.  Used by the bandwidth-curve tool.
@@ -155,8 +169,11 @@ class FusedEngine {
   bool use_nvls_ = true;
   bool use_nvls_rs_ = false;
   void carve_workspace(long long elems);
+  void gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M, int first_row,
+                     const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream);
   unsigned long long* phase_trace_ = nullptr;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
+  void* ag_dst_scratch_[kMaxRanks] = {};  // destination of this rank's block on every rank (per call)
   unsigned long long pushes_ = 0;  // arrivals expected at the push counter so far
 };
 

@@ -57,6 +57,17 @@ def allgather_gemm(impl, a_shard, b, world_size: int, algo: int = 0, out: Option
     return out
 
 
+def a2a_dispatch_gemm(impl, a_send, b, mlen_cpu: torch.Tensor, rank: int, algo: int = 0):
+    """Fused all-to-all dispatch + GEMM: ``mlen_cpu[i][j]`` rows travel from rank i
+    to rank j (``a_send`` holds this rank's rows in destination order); returns
+    the product of the rows received here, in source order, with ``b^T``."""
+    _check(a_send)
+    m_pad = impl.a2a_padded_rows(mlen_cpu, algo)
+    out = torch.empty((m_pad, b.size(0)), dtype=a_send.dtype, device=a_send.device)
+    impl.a2a_dispatch_gemm(a_send, b, out, mlen_cpu, algo)
+    return out[: int(mlen_cpu[:, rank].sum())]
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     _check(x)
     out = torch.empty_like(x)

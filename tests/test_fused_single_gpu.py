@@ -157,3 +157,21 @@ def test_allgather_gemm_world1():
         impl.check_status()
         ref = A.float() @ B.float().t()
         assert (C.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item()
+
+
+def test_a2a_dispatch_gemm_world1():
+    K, N = 128, 256
+    impl = make_impl()
+    mlen = torch.tensor([[300]], dtype=torch.int32)
+    A = torch.randn(300, K, device="cuda", dtype=torch.float16)
+    B = (torch.randn(N, K, device="cuda") / K ** 0.5).half()
+    m_pad = impl.a2a_padded_rows(mlen, 0)
+    assert m_pad == 384
+    C = torch.empty(m_pad, N, device="cuda", dtype=torch.float16)
+    impl.a2a_dispatch_gemm(A, B, C, mlen, 0)
+    torch.cuda.synchronize()
+    impl.check_status()
+    ref = A.float() @ B.float().t()
+    assert (C[:300].float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
+    with pytest.raises(RuntimeError):
+        impl.a2a_dispatch_gemm(A[:100], B, C, mlen, 0)  # fewer rows than mLen says
