@@ -332,6 +332,114 @@ __device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem
 }
 
 // ---------------------------------------------------------------------------
+// reduce phase on a single GPU with RMSNorm: rows streamed through shared memory
+// ---------------------------------------------------------------------------
+// With one rank there is nothing to sum: the phase is RMSNorm over the product
+// the epilogue stored.  Eight warps per SM cannot hide memory latency with
+// register loads, so each warp keeps two row buffers in shared memory and lets
+// the bulk-copy engine fetch row i+1 (cp.async.bulk, completion on an mbarrier)
+// while it normalises row i out of shared memory.  Returns false without doing
+// anything when shared memory cannot hold two rows per warp for at least one
+// warp (the caller then takes the generic path).
+template <bool BF16>
+__device__ __forceinline__ bool reduce_phase_single(const FusedParams& p, uint8_t* smem, int smem_bytes,
+                                                    uint64_t* rbar, int warp, int lane, uint64_t deadline,
+                                                    volatile uint32_t* abort_flag) {
+  constexpr int BM = 128;
+  constexpr int kWarps = kThreads / 32;
+  const int n_chunks = p.N >> 3;
+  const int row_bytes = p.N * 2;
+  int active = ((smem_bytes - row_bytes) / row_bytes) / 2;  // warps that get two row buffers after the weight vector
+  if (active > kWarps) active = kWarps;
+  if (active < 1) return false;
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint16_t* gamma = reinterpret_cast<const uint16_t*>(p.gamma);
+  for (int c = threadIdx.x; c < n_chunks; c += kThreads) {
+    ptx::st_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4), *reinterpret_cast<const uint4*>(gamma + c * 8));
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2 * kWarps; ++i) ptx::mbar_init(&rbar[i], 1);
+    ptx::mbar_fence_init();
+    ptx::fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (warp >= active) return true;
+  const uint32_t buf0 = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(1 + 2 * warp);
+  uint64_t* bar = rbar + 2 * warp;
+  const int rows_local = p.rows_per_owner;
+  const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
+  const uint32_t* my_flag = p.flag[p.me];
+  auto row_of = [&](int i) { return static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (warp + active * i); };
+
+  // lane 0: wait for the row's tile row, then start the copy of row i into buffer b
+  auto issue = [&](int i, int b) -> uint32_t {
+    const int lr = row_of(i);
+    if (lr >= rows_local) return 1u;
+    uint32_t seen = 0;
+    if (!ptx::wait_counter_geq(my_flag + lr / BM, p.flag_target, deadline, &seen)) {
+      report_error(p.status, ST_TIMEOUT_FLAG, p.me, lr / BM, seen, p.flag_target);
+      *abort_flag = 1;
+      return 0u;
+    }
+    ptx::fence_proxy_async_all();  // the epilogue's generic-proxy stores before the async-proxy read
+    ptx::mbar_arrive_expect_tx(&bar[b], static_cast<uint32_t>(row_bytes));
+    ptx::bulk_load_1d(buf0 + static_cast<uint32_t>(b * row_bytes), stage + static_cast<long long>(lr) * p.N,
+                      static_cast<uint32_t>(row_bytes), &bar[b]);
+    return 1u;
+  };
+
+  uint32_t ok = 1;
+  if (lane == 0) ok = issue(0, 0);
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  uint32_t phases = 0;  // bit b: parity to wait for on buffer b
+  for (int i = 0; ok; ++i) {
+    const int lr = row_of(i);
+    if (lr >= rows_local) break;
+    const int b = i & 1;
+    // all lanes finished reading buffer b^1 (row i-1) at the __syncwarp below
+    if (lane == 0) ok = issue(i + 1, b ^ 1);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ptx::mbar_wait(&bar[b], (phases >> b) & 1u, deadline)) {
+      if (lane == 0) {
+        report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x600u + warp, i, lr);
+        *abort_flag = 1;
+      }
+      break;
+    }
+    phases ^= 1u << b;
+    const uint32_t rowbuf = buf0 + static_cast<uint32_t>(b * row_bytes);
+    float ssq = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < n_chunks; c += 32) {
+      const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
+      float2 f;
+      f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
+      f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
+      f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
+      f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
+#pragma unroll 4
+    for (int c = lane; c < n_chunks; c += 32) {
+      const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
+      const uint4 w = ptx::ld_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4));
+      float2 f;
+      uint4 o;
+      f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
+      f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
+      f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
+      f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
+      ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[0]) + layout_offset(p.out_layout, lr, c * 8), o);
+    }
+    __syncwarp();
+    if (p.bcast && lane == 0 && p.done[0] != nullptr) ptx::red_release_sys_add(p.done[0], 1u);
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
 template <int BN, bool BF16, int CTAS>
@@ -734,8 +842,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   // ===================== reduce phase =====================
   ptx::fence_proxy_async_smem();  // the pipeline's shared memory is reused through the generic proxy
   constexpr int kRowSmem = T::STAGES * T::STAGE_BYTES + T::EPI_BYTES;
+  // barriers of the single-GPU row pipeline: behind the partial-sum scratch
+  uint64_t* rbar = bars + 48;
   if (p.nvls) {
     reduce_phase<BF16, 1, true>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag);
+  } else if (p.ws == 1 && p.norm && p.reduce_group == 1 &&
+             reduce_phase_single<BF16>(p, smem, kRowSmem, rbar, warp, lane, deadline, abort_flag)) {
+    // done: rows streamed through shared memory
   } else {
     switch (p.ws) {
       case 1: reduce_phase<BF16, 1, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;

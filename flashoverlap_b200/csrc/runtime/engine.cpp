@@ -208,7 +208,8 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
     p.mc_out = heap_.mc(ws_.result[set]);
     p.mc_done = static_cast<uint32_t*>(heap_.mc(ws_.flags[set])) + kMaxTileRows;
   }
-  if (p.raster_group == 0) p.raster_group = 2;
+  // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
+  if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
@@ -267,7 +268,8 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
     // ranks push to different owners
     p.rot = ((rank_ + 1) % world_) * (rows_local / tc.bm);
   }
-  if (p.raster_group == 0) p.raster_group = 2;
+  // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
+  if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
