@@ -1,0 +1,69 @@
+"""The two search drivers on CPU with the GPU-side measurements replaced by a
+deterministic fake: both must pick the same solution (exhaustive times every
+candidate, predictive times only its best-ranked few) and write a valid stage-2
+file in the reference's format."""
+import json
+
+import pytest
+import torch
+
+from flashoverlap_b200.tune import search
+from flashoverlap_b200.utils import config as cfg
+
+
+def fake_time(algo, raster, reduce_group):
+    # Algo 3 fastest, raster 2 and the automatic reduce group best
+    return 0.2 + 0.01 * abs(algo - 3) + 0.002 * abs(raster - 2) + 0.001 * reduce_group
+
+
+@pytest.fixture
+def patched(monkeypatch, tmp_path):
+    calls = []
+
+    def perf_running(impl, M, N, K, BM, BN, algo, cseg, hint, comm_op, dtype=None, warmup=0, reps=0, raster_group=0,
+                     reduce_group=0):
+        calls.append((algo, raster_group, reduce_group))
+        return fake_time(algo, raster_group, reduce_group)
+
+    def compute_hint(impl, M, N, K, BM, BN, algo, wave, comm_op, dtype=None, **kw):
+        tiles = (M // BM) * (N // BN)
+        return True, list(reversed(range(tiles)))
+
+    monkeypatch.setattr(search, "perf_running", perf_running)
+    monkeypatch.setattr(search, "compute_hint", compute_hint)
+    monkeypatch.setattr(search, "sm_count", lambda: 148)
+    monkeypatch.setattr(search, "world", lambda: (0, 8))
+    monkeypatch.setattr(cfg, "gpu_tag", lambda name=None: "b200")
+    M, N, K = 4096, 8192, 1024
+    cfg.save_stage1(M, N, K, [256, 128, 128], [256, 256, 128], [0.054, 0.057, 0.08], [3, 0, 1], tmp_path)
+    return calls, tmp_path, (M, N, K)
+
+
+def test_exhaustive_and_predictive_agree(patched):
+    calls, path, (M, N, K) = patched
+    ex = search.exhaustive_search(None, M, N, K, "all_reduce", path=path, verbose=False)
+    n_exhaustive = len(calls)
+    assert ex["Algo"] == 3 and ex["raster_group"] == 2 and ex["reduce_group"] == 0
+    # re-running from the stage-2 file works because the stage-1 lists are kept
+    calls.clear()
+    curve = torch.tensor([[2.0 ** 20, 150.0], [2.0 ** 26, 420.0]])
+    pr = search.predictive_search(None, M, N, K, "all_reduce", curve, 550.0, path=path, verbose=False)
+    assert len(calls) <= 3 < n_exhaustive
+    assert (pr["Algo"], pr["raster_group"]) == (ex["Algo"], ex["raster_group"])
+    data = json.load(open(cfg.json_path(M, N, K, path)))
+    cfg.validate_stage2(data, M, N)
+    tiles = (M // 256) * (N // 256)
+    assert sum(data["cSeg"]) == tiles and data["rLDN"] == 1 and len(data["hint"]) == tiles
+    assert data["search"] == "predictive" and data["stage1"]["Algo"] == [3, 0, 1]
+
+
+def test_search_fails_loudly_without_consistent_hint(patched, monkeypatch):
+    calls, path, (M, N, K) = patched
+    monkeypatch.setattr(search, "compute_hint", lambda *a, **k: (False, []))
+    with pytest.raises(RuntimeError, match="tuning failed"):
+        search.exhaustive_search(None, M, N, K, "all_reduce", path=path, verbose=False)
+
+
+def test_knob_candidates_cover_defaults():
+    c = search.knob_candidates(4096, 8)
+    assert (2, 0) in c and (1, 1) in c and all(rg in search.RASTER_CHOICES for rg, _ in c)
