@@ -116,6 +116,8 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("nccl_all2all", &OverlapImpl::NcclAll2All)
       .def("mccl_all2all", &OverlapImpl::NcclAll2All)
       .def("seg_allreduce", &OverlapImpl::SegAllReduce)
+      .def("gemm_allreduce_twostream", &OverlapImpl::GemmAllReduceTwoStream)
+      .def("gemm_reducescatter_twostream", &OverlapImpl::GemmReduceScatterTwoStream)
       .def("gemm_allreduce_fused", &OverlapImpl::GemmAllReduceFused)
       .def("gemm_reducescatter_fused", &OverlapImpl::GemmReduceScatterFused)
       .def("gemm_rmsnorm", &OverlapImpl::GemmRmsNorm)

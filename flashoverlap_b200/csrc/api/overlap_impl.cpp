@@ -3,6 +3,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <cuda.h>
+
 #include "checks.h"
 
 namespace fo {
@@ -62,7 +64,10 @@ void check_segments(const at::Tensor& cSEG_CPU, const at::Tensor& cSEG_GPU, int6
 }  // namespace
 
 OverlapImpl::OverlapImpl() = default;
-OverlapImpl::~OverlapImpl() = default;
+OverlapImpl::~OverlapImpl() {
+  if (join_event_ != nullptr) cudaEventDestroy(join_event_);
+  if (comm_stream_ != nullptr) cudaStreamDestroy(comm_stream_);
+}
 
 void OverlapImpl::require_comm(const char* op) const {
   TORCH_CHECK(comm_.world() == 1 || comm_.active(), op, ": call nccl_init first");
@@ -304,6 +309,123 @@ void OverlapImpl::SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum
     FO_NCCL_CHECK(ncclAllReduce(ptr, ptr, n, nccl_type(C), ncclSum, comm_.get(), current_stream()));
     done += n;
   }
+}
+
+namespace {
+using StreamWaitFn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+StreamWaitFn stream_wait_value32() {
+  static StreamWaitFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<StreamWaitFn>(ptr);
+    }
+  }
+  return fn;
+}
+}  // namespace
+
+void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Tensor& C, at::Tensor* D, at::Tensor& MM,
+                             at::Tensor& RA, at::Tensor* RE, int64_t rLDN, at::Tensor& cSEG_CPU, at::Tensor& cSEG_GPU,
+                             int64_t algo, int64_t gemm_ctas) {
+  check_gemm_args(A, B, &C);
+  require_comm("two-stream overlap");
+  c10::cuda::CUDAGuard guard(A.device());
+  GemmOperands g = operands(A, B, algo);
+  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
+  const int64_t tiles = RA.numel();
+  check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), false);
+  const int ws = comm_.world();
+  const TileConfig tc = algo_config(g.algo);
+  if (scatter) {
+    TORCH_CHECK(D != nullptr && RE != nullptr, "reduce-scatter needs D and RE");
+    check_int_tensor(*RE, "RE", true);
+    TORCH_CHECK(D->is_cuda() && D->is_contiguous() && D->scalar_type() == A.scalar_type() &&
+                    D->numel() * ws == C.numel(),
+                "D must hold M*N/size elements of A's dtype");
+    TORCH_CHECK(L.bm % ws == 0, "BM must be divisible by the world size");
+    TORCH_CHECK(rLDN == 1, "the row map is defined for rLDN == 1");
+    TORCH_CHECK(RE->numel() == static_cast<int64_t>(g.M) * g.N / L.bn, "RE must have M*N/BN entries");
+    if (RE->data_ptr() != checked_row_map_) {  // the epilogue stores through this map: check it once per tensor
+      TORCH_CHECK(RE->min().item<int>() >= 0 && RE->max().item<int>() < RE->numel(), "RE holds a row outside the buffer");
+      checked_row_map_ = RE->data_ptr();
+    }
+  }
+  auto wait_fn = stream_wait_value32();
+  TORCH_CHECK(wait_fn != nullptr, "cuStreamWaitValue32 is not available from this driver");
+  if (comm_stream_ == nullptr) {
+    int lo = 0, hi = 0;
+    FO_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    FO_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
+    FO_CUDA_CHECK(cudaEventCreateWithFlags(&join_event_, cudaEventDisableTiming));
+  }
+  cudaStream_t stream = current_stream();
+  // the collectives may start only after earlier work on the caller's stream (inputs, previous use of C / MM)
+  FO_CUDA_CHECK(cudaEventRecord(join_event_, stream));
+  FO_CUDA_CHECK(cudaStreamWaitEvent(comm_stream_, join_event_, 0));
+
+  SignalArgs sig;
+  sig.seg_counter = MM.data_ptr<int>();
+  sig.cseg = cSEG_GPU.data_ptr<int>();
+  sig.nseg = static_cast<int>(cSEG_GPU.numel());
+  sig.slot_of_tile = RA.data_ptr<int>();
+  int ctas = static_cast<int>(gemm_ctas);
+  if (ctas <= 0) ctas = device_sm_count() - 16;
+  if (tc.ctas == 2) ctas &= ~1;
+  TORCH_CHECK(ctas >= tc.ctas, "too few CTAs for the GEMM");
+  g.sm_count = ctas;
+  if (scatter) {
+    // rows of every tile grouped by (row % size), segment by segment: what the
+    // reference's scatter epilogue writes through its row map RE
+    OutLayout LS = L;
+    LS.row_map = RE->data_ptr<int>();
+    engine_.gemm(g, C.data_ptr(), &LS, &sig, stream);
+  } else {
+    engine_.gemm(g, C.data_ptr(), &L, &sig, stream);
+  }
+  const int* seg = cSEG_CPU.data_ptr<int>();
+  const size_t tile_elems = static_cast<size_t>(L.bm) * L.bn;
+  const size_t esz = C.element_size();
+  size_t done = 0;
+  for (int64_t i = 0; i < cSEG_CPU.numel(); ++i) {
+    const size_t count = tile_elems * static_cast<size_t>(seg[i]);
+    CUresult r = wait_fn(reinterpret_cast<CUstream>(comm_stream_),
+                         reinterpret_cast<CUdeviceptr>(MM.data_ptr<int>() + i),
+                         static_cast<cuuint32_t>(seg[i] * tc.ctas), CU_STREAM_WAIT_VALUE_GEQ);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuStreamWaitValue32 failed with ", static_cast<int>(r));
+    char* src = static_cast<char*>(C.data_ptr()) + done * esz;
+    if (comm_.active()) {
+      if (scatter) {
+        char* dst = static_cast<char*>(D->data_ptr()) + done / ws * esz;
+        FO_NCCL_CHECK(ncclReduceScatter(src, dst, count / ws, nccl_type(C), ncclSum, comm_.get(), comm_stream_));
+      } else {
+        FO_NCCL_CHECK(ncclAllReduce(src, src, count, nccl_type(C), ncclSum, comm_.get(), comm_stream_));
+      }
+    } else if (scatter) {
+      FO_CUDA_CHECK(cudaMemcpyAsync(D->data_ptr(), C.data_ptr(), C.nbytes(), cudaMemcpyDeviceToDevice, comm_stream_));
+    }
+    done += count;
+  }
+  // the counters return to zero (the reference's wait kernel swaps them back on success)
+  FO_CUDA_CHECK(cudaMemsetAsync(MM.data_ptr<int>(), 0, sizeof(int) * cSEG_CPU.numel(), comm_stream_));
+  FO_CUDA_CHECK(cudaEventRecord(join_event_, comm_stream_));
+  FO_CUDA_CHECK(cudaStreamWaitEvent(stream, join_event_, 0));
+}
+
+void OverlapImpl::GemmAllReduceTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA,
+                                         int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo,
+                                         int64_t gemm_ctas) {
+  two_stream(false, A, B, C, nullptr, MM, RA, nullptr, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas);
+}
+
+void OverlapImpl::GemmReduceScatterTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, at::Tensor MM,
+                                             at::Tensor RA, at::Tensor RE, int64_t rLDN, at::Tensor cSEG_CPU,
+                                             at::Tensor cSEG_GPU, int64_t algo, int64_t gemm_ctas) {
+  two_stream(true, A, B, C, &D, MM, RA, &RE, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas);
 }
 
 at::Tensor OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, c10::optional<at::Tensor> weight, double eps,

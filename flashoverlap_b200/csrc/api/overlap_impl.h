@@ -40,6 +40,20 @@ class OverlapImpl : public torch::CustomClassHolder {
   void NcclAll2All(at::Tensor C, at::Tensor D, at::Tensor mLen_CPU);
   void SegAllReduce(at::Tensor C, at::Tensor cSEG_CPU, int64_t SegNum);
 
+  // ---- the reference's own overlap design, restated for B200 ---------------
+  // Comparator, not the product: a signalling GEMM on the current stream counts
+  // finished tiles per segment in MM; a second, high-priority stream waits for
+  // each segment's count with a stream memory operation (cuStreamWaitValue32:
+  // no kernel spins, unlike the reference's kernel_wait_flag) and then runs
+  // NCCL all-reduce / reduce-scatter on that segment of the tile-reordered
+  // buffer (reference: src/overlap_impl.cu:221-328).  `gemm_ctas` CTAs compute
+  // (0 = SM count - 16, leaving SMs to the NCCL kernels).  MM is left at zero.
+  void GemmAllReduceTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA, int64_t rLDN,
+                              at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo, int64_t gemm_ctas);
+  void GemmReduceScatterTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, at::Tensor MM,
+                                  at::Tensor RA, at::Tensor RE, int64_t rLDN, at::Tensor cSEG_CPU,
+                                  at::Tensor cSEG_GPU, int64_t algo, int64_t gemm_ctas);
+
   // ---- fused entry points with natural-order results ----------------------
   // GEMM + all-reduce (+ RMSNorm when `weight` is given).  Returns a tensor
   // that aliases the symmetric result buffer (valid until the second next
@@ -96,8 +110,14 @@ class OverlapImpl : public torch::CustomClassHolder {
   GemmOperands operands(const at::Tensor& A, const at::Tensor& B, int64_t algo) const;
   void require_comm(const char* op) const;
 
+  void two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Tensor& C, at::Tensor* D, at::Tensor& MM,
+                  at::Tensor& RA, at::Tensor* RE, int64_t rLDN, at::Tensor& cSEG_CPU, at::Tensor& cSEG_GPU,
+                  int64_t algo, int64_t gemm_ctas);
   Communicator comm_;
   FusedEngine engine_;
+  cudaStream_t comm_stream_ = nullptr;
+  cudaEvent_t join_event_ = nullptr;
+  const void* checked_row_map_ = nullptr;
   bool engine_ready_ = false;
   at::Tensor phase_trace_;
 };

@@ -25,11 +25,15 @@ constexpr int kMaxRanks = 8;
 //   the matrix is cut into bm x bn tiles, tile t = (row/bm)*tn + col/bn lives in
 //   slot s = ra[t]; with w = rldn*bn the element sits at
 //   ((s / rldn) * bm + row % bm) * w + (s % rldn) * bn + col % bn.
+//   With row_map (only with rldn == 1) the row index of that view goes through
+//   the map first: the reference's scatter epilogue, which groups the rows of a
+//   segment by (row % world) (reference: src/overlap/gemm_with_scatter.h:161-177).
 struct OutLayout {
   int tiled;
   int bm, bn, tn, rldn;
   const int* ra;
   long long ld;
+  const int* row_map;
 };
 
 enum OwnMode : int {

@@ -64,7 +64,9 @@ __device__ __forceinline__ long long layout_offset(const OutLayout& L, int row, 
   const int t = (row / L.bm) * L.tn + col / L.bn;
   const int s = L.ra ? L.ra[t] : t;
   const long long w = static_cast<long long>(L.rldn) * L.bn;
-  return (static_cast<long long>(s / L.rldn) * L.bm + row % L.bm) * w + (s % L.rldn) * L.bn + col % L.bn;
+  long long view_row = static_cast<long long>(s / L.rldn) * L.bm + row % L.bm;
+  if (L.row_map != nullptr) view_row = L.row_map[view_row];
+  return view_row * w + (s % L.rldn) * L.bn + col % L.bn;
 }
 
 __device__ __forceinline__ void report_error(StatusWord* st, uint32_t code, uint32_t rank, uint32_t where,
@@ -797,19 +799,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
             ptx::red_relaxed_sys_add(p.flag[0] + flag_blk, 1u);
           }
         }
-        if (cta_rank == 0 && (p.seg_counter != nullptr || p.ticket_counter != nullptr)) {
-          // Reference-compatible bookkeeping, once per tile.
+        if (p.seg_counter != nullptr || p.ticket_counter != nullptr) {
+          // Reference-compatible bookkeeping.
           const int tile_id = m_blk * p.TN + n_blk;
           const int slot = p.slot_of_tile ? p.slot_of_tile[tile_id] : tile_id;
           if (p.seg_counter != nullptr) {
+            // Segment counters gate work on another stream of this GPU: every
+            // CTA counts its own part of the tile (a CTA pair adds 2 per tile)
+            // once its stores are visible device-wide.
             int seg = 0, acc = 0;
             for (; seg < p.nseg; ++seg) {
               acc += p.cseg[seg];
               if (slot < acc) break;
             }
+            ptx::fence_acq_rel_gpu();
             if (seg < p.nseg) atomicAdd(p.seg_counter + seg, 1);
           }
-          if (p.ticket_counter != nullptr) {
+          if (cta_rank == 0 && p.ticket_counter != nullptr) {  // completion order, once per tile
             const int ticket = atomicAdd(p.ticket_counter, 1);
             if (slot >= 0 && slot < num_tiles) p.trace[slot] = ticket;
             else report_error(p.status, ST_BAD_INDEX, p.me, 0x500u, slot, num_tiles);

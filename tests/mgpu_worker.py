@@ -190,6 +190,23 @@ def main():
     torch.cuda.synchronize()
     check("compat gemm_reducescatter_overlap", from_tile_order(D, bm // world, bn, RA), ref[rank::world], 5e-2)
 
+    # the reference's two-stream design (comparator): signalling GEMM + stream waits + segmented NCCL
+    MM.zero_()
+    C = torch.full((M, N), float("nan"), device=dev, dtype=torch.float16)
+    for rep in range(2):
+        impl.gemm_allreduce_twostream(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, 0)
+    torch.cuda.synchronize()
+    check("two-stream comparator all-reduce (reordered)", from_tile_order(C, bm, bn, RA), ref, 1e-2)
+    D = torch.full((M // world, N), float("nan"), device=dev, dtype=torch.float16)
+    for rep in range(2):
+        impl.gemm_reducescatter_twostream(A, B, Ctmp, D, MM, RA, RE, 1, cseg_cpu, cseg_gpu, algo, 0)
+    torch.cuda.synchronize()
+    check("two-stream comparator reduce-scatter", from_tile_order(D, bm // world, bn, RA), ref[rank::world], 5e-2)
+    ok = int(MM.abs().sum()) == 0
+    if rank == 0:
+        print(f"{'PASS' if ok else 'FAIL'} two-stream comparator leaves the counters at zero", flush=True)
+    failures += 0 if ok else 1
+
     # non-overlapped paths and the cuBLAS + NCCL baseline
     base = make_baseline_impl()
     C1 = torch.empty((M, N), device=dev, dtype=torch.float16)
