@@ -43,7 +43,7 @@ uint32_t* FusedEngine::done_ptr(int rank, int set) const { return flag_ptr(rank,
 namespace {
 size_t workspace_bytes(long long elems) {
   const size_t mat = static_cast<size_t>(elems) * 2;
-  return 4 * (mat + 4096) + 2 * (kFlagWords * 4 + 4096) + 8192 + (1 << 20);
+  return 4 * (mat + 4096) + 3 * (kFlagWords * 4 + 4096) + 8192 + (1 << 20);
 }
 }  // namespace
 
@@ -54,6 +54,7 @@ void FusedEngine::carve_workspace(long long elems) {
   for (int s = 0; s < 2; ++s) ws_.result[s] = heap_.alloc(mat, 1024);
   for (int s = 0; s < 2; ++s) ws_.flags[s] = heap_.alloc(kFlagWords * 4, 1024);
   ws_.misc = heap_.alloc(4096, 1024);
+  ws_.local_flags = heap_.alloc(kFlagWords * 4, 1024);
   ws_.capacity_elems = elems;
   calls_ = 0;
   pushes_ = 0;
@@ -148,8 +149,11 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
   if (g.M / 128 > kMaxTileRows) throw std::runtime_error("gemm_rmsnorm: too many tile rows");
-  const int set = static_cast<int>(calls_ & 1ull);
-  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  // A purely local operation: it uses its own counters, cleared right before the
+  // launch, and does not take part in the alternation of the shared sets (it
+  // does not synchronise the ranks, so it must not advance their call count).
+  uint32_t* local = static_cast<uint32_t*>(heap_.local(ws_.local_flags));
+  check(cudaMemsetAsync(local, 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
   FusedParams p;
   base_params(p, nullptr);
   p.own_mode = OWN_SINGLE;
@@ -158,8 +162,8 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   p.rows_per_owner = g.M;
   p.epi_base[0] = scratch;
   p.epi_layout.ld = g.N;
-  p.flag[0] = flag_ptr(rank_, set);
-  if (p.raster_group == 0) p.raster_group = 4;
+  p.flag[0] = local;
+  if (p.raster_group == 0) p.raster_group = 8;
   p.reduce = 1;
   p.stage = scratch;
   p.flag_target = static_cast<uint32_t>(g.N / tc.bn);
@@ -171,7 +175,6 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   p.out_layout.ld = g.N;
   const char* why = nullptr;
   check_launch(launch_fused(g, p, stream, &why), why, "gemm_rmsnorm");
-  ++calls_;
 }
 
 void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, const NormArgs& norm,
@@ -294,8 +297,11 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
                                 int first_row, const void* B, void* C, int N, int K, DType dtype, int algo,
                                 const char* op, cudaStream_t stream) {
   const TileConfig tc = algo_config(algo);
-  const int set = static_cast<int>(calls_ & 1ull);
-  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  // A purely local operation: it uses its own counters, cleared right before the
+  // launch, and does not take part in the alternation of the shared sets (it
+  // does not synchronise the ranks, so it must not advance their call count).
+  uint32_t* local = static_cast<uint32_t*>(heap_.local(ws_.local_flags));
+  check(cudaMemsetAsync(local, 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
   FusedParams p;
   base_params(p, nullptr);
   GemmOperands g{};

@@ -151,6 +151,7 @@ class FusedEngine {
     size_t result[2] = {0, 0};
     size_t flags[2] = {0, 0};  // kMaxTileRows arrival counters + 1 delivery counter each
     size_t misc = 0;           // counters that the per-call clearing must not touch
+    size_t local_flags = 0;    // arrival counters of single-GPU operations (never written by peers)
     long long capacity_elems = 0;
   };
   void base_params(FusedParams& p, const SignalArgs* sig);
