@@ -97,6 +97,10 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         ldflags += [f"-L{cublas / 'lib'}", "-l:libcublas.so.12", f"-Wl,-rpath,{cublas / 'lib'}"]
     else:
         ldflags += ["-lcublas"]
+    # A digest left over from an earlier build must not vouch for a library this
+    # build fails to replace.
+    if _DIGEST.exists():
+        _DIGEST.unlink()
     cpp_extension.load(
         name=_LIBNAME,
         sources=[str(p) for p in _existing_sources()],
@@ -110,6 +114,11 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     )
     if not _LIB.exists():
         raise RuntimeError(f"flashoverlap_b200: build finished but {_LIB} is missing")
+    newest = max(p.stat().st_mtime for p in _CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h"})
+    if _LIB.stat().st_mtime < newest:
+        # (a retry after a failed build in the same process makes torch skip the build and load the old file)
+        raise RuntimeError(f"flashoverlap_b200: {_LIB} is older than its sources: the build did not replace it; "
+                           "run `python -m flashoverlap_b200._build --force` in a fresh process to see the compiler error")
     _DIGEST.write_text(_source_digest() + "\n")
     return _LIB
 

@@ -377,9 +377,10 @@ __device__ __forceinline__ bool reduce_phase_single(const FusedParams& p, uint8_
   auto issue = [&](int i, int b) -> uint32_t {
     const int lr = row_of(i);
     if (lr >= rows_local) return 1u;
+    const int rb = lr / BM;
     uint32_t seen = 0;
-    if (!ptx::wait_counter_geq(my_flag + lr / BM, p.flag_target, deadline, &seen)) {
-      report_error(p.status, ST_TIMEOUT_FLAG, p.me, lr / BM, seen, p.flag_target);
+    if (!ptx::wait_counter_geq(my_flag + rb, p.flag_target, deadline, &seen)) {
+      report_error(p.status, ST_TIMEOUT_FLAG, p.me, rb, seen, p.flag_target);
       *abort_flag = 1;
       return 0u;
     }

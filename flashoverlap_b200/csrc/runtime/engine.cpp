@@ -297,11 +297,8 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
                                 int first_row, const void* B, void* C, int N, int K, DType dtype, int algo,
                                 const char* op, cudaStream_t stream) {
   const TileConfig tc = algo_config(algo);
-  // A purely local operation: it uses its own counters, cleared right before the
-  // launch, and does not take part in the alternation of the shared sets (it
-  // does not synchronise the ranks, so it must not advance their call count).
-  uint32_t* local = static_cast<uint32_t*>(heap_.local(ws_.local_flags));
-  check(cudaMemsetAsync(local, 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  const int set = static_cast<int>(calls_ & 1ull);
+  check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
   FusedParams p;
   base_params(p, nullptr);
   GemmOperands g{};
