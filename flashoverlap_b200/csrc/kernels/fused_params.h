@@ -3,9 +3,9 @@
 // One kernel covers what the reference spreads over a signalling GEMM, a
 // counting kernel and a series of NCCL calls (reference: src/overlap_impl.cu:221-328,
 // src/overlap/gemm_with_signal.h:127-202, src/overlap/gemm_with_scatter.h:127-197,
-// src/wait.cuh:5-9).  The GEMM phase writes every finished 32-row slab of an
-// output tile where its consumer needs it (own memory or a peer's staging
-// buffer) and bumps a counter on the owning GPU; the reduce phase, run by the
+// src/wait.cuh:5-9).  The GEMM phase writes every finished tile where its
+// consumer needs it (own memory or a peer's staging buffer) and bumps a counter
+// per 128-row block on the owning GPU; the reduce phase, run by the
 // same CTAs once they are out of tiles, waits (bounded) on those counters, sums
 // the per-rank partials in fp32, optionally applies RMSNorm and writes the
 // result locally (reduce-scatter) or to every peer (all-reduce).
@@ -51,7 +51,8 @@ enum StatusCode : uint32_t {
   ST_TIMEOUT_GATHER = 5,  // an all-gathered operand shard never arrived
 };
 
-// Written by the device on the first error only; lives in mapped host memory.
+// Written by the device on the first error only; lives in device memory and is
+// read back by FusedEngine::read_status.
 struct StatusWord {
   uint32_t code;
   uint32_t rank;

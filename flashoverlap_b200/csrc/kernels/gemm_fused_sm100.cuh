@@ -4,16 +4,21 @@
 // through peer-to-peer stores and system-scope counters.
 //
 // CTA layout (256 threads, one CTA per SM, grid <= number of SMs):
-//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads)
+//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads; with a
+//                               gathered A operand it first waits for the source
+//                               ranks whose rows the tile needs)
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma / tcgen05.commit)
-//   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end)
+//   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end);
+//                               in all-gather / all-to-all mode it then pushes this
+//                               rank's rows of A to the other ranks
 //   warp 3      signalling     (one lane publishes finished tiles at system scope
 //                               and bumps the owners' arrival counters)
+//   warps 4-7   epilogue       (tcgen05.ld -> convert -> smem transpose ->
+//                               coalesced 16-byte stores, local or to a peer)
 // With CTAS == 2 two such CTAs form a cluster: both stage operands and run an
 // epilogue for their own 128 rows, the MMA warp of rank 0 issues for the pair.
-//   warps 4-7   epilogue       (tcgen05.ld -> convert -> smem transpose ->
-//                               coalesced 16-byte stores)
-// After its last tile the whole CTA joins the reduce phase (one row per warp).
+// After its last tile the whole CTA joins the reduce phase: groups of 1, 2, 4 or
+// 8 warps take one owned row at a time.
 //
 // Replaces, as one launch, the reference's signalling GEMM + wait kernel +
 // segmented NCCL calls (reference: src/overlap_impl.cu:221-328).
@@ -133,16 +138,18 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
 }
 
 // ---------------------------------------------------------------------------
-// reduce phase: one warp per owned row
+// reduce phase: a group of G warps per owned row (G = p.reduce_group)
 // ---------------------------------------------------------------------------
-// Each warp of the CTA takes one row at a time: it waits (bounded) until the
-// partial rows of every rank have arrived, sums them in fp32 and rounds the
-// sum to the 16-bit type (the value an all-reduce would have produced).
-// Without RMSNorm the rounded sum goes straight to its destination(s); with
-// RMSNorm it is parked in shared memory while the warp accumulates the sum of
-// squares, then scaled, multiplied by the weight and written out.  Warps never
-// synchronise with one another, so every SM keeps several independent chains
-// of loads in flight.  WS > 0 fixes the number of ranks at compile time (all
+// Each group takes one row at a time: its warps wait (bounded) until the
+// partial rows of every rank have arrived, sum them in fp32 and round the sum
+// to the 16-bit type (the value an all-reduce would have produced).  Without
+// RMSNorm the rounded sum goes straight to its destination(s); with RMSNorm it
+// is parked in shared memory while the sum of squares is accumulated (combined
+// across the group's warps through a named barrier when G > 1), then scaled,
+// multiplied by the weight and written out.  Groups never synchronise with one
+// another, so every SM keeps several independent chains of loads in flight.
+// NVLS == true replaces the per-rank loads by one multimem.ld_reduce per chunk
+// and the per-rank result stores by one multimem.st.  WS > 0 fixes the number of ranks at compile time (all
 // loads of a batch are issued before the first use); WS == 0 is the generic
 // fallback for other group sizes.
 template <bool BF16, int WS, bool NVLS>
