@@ -175,3 +175,21 @@ def test_a2a_dispatch_gemm_world1():
     assert (C[:300].float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
     with pytest.raises(RuntimeError):
         impl.a2a_dispatch_gemm(A[:100], B, C, mlen, 0)  # fewer rows than mLen says
+
+
+def test_host_feeder_double_buffers_inputs():
+    from flashoverlap_b200.utils.pipeline import HostFeeder
+
+    feeder = HostFeeder((64, 32), torch.float16)
+    batches = [torch.full((64, 32), float(i), dtype=torch.float16).pin_memory() for i in range(5)]
+    feeder.submit(batches[0])
+    seen = []
+    for i in range(1, 6):
+        x = feeder.take()
+        if i < 5:
+            feeder.submit(batches[i])
+        y = x.float().mean()  # stands for the step's compute
+        feeder.release(x)
+        seen.append(y)
+    torch.cuda.synchronize()
+    assert [float(v) for v in seen] == [0.0, 1.0, 2.0, 3.0, 4.0]
