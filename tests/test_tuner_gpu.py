@@ -1,0 +1,50 @@
+"""The tuning pipeline end to end on one GPU (world size 1): tile profiling,
+bandwidth-curve file, completion-order hint, predictive and exhaustive search,
+stage-2 file consumed by the reference-compatible layer."""
+import pytest
+import torch
+
+import flashoverlap_b200  # noqa: F401
+from flashoverlap_b200.models import OverlapRowParallelLayer, ReorderRMSNorm
+from flashoverlap_b200.parallel import make_overlap_impl
+from flashoverlap_b200.tune import search
+from flashoverlap_b200.tune.runtime import compute_hint, profile_gemm
+from flashoverlap_b200.utils import config as cfg
+
+pytestmark = pytest.mark.gpu
+
+
+def test_profile_hint_search_and_use(tmp_path):
+    M, N, K = 1024, 2048, 256
+    impl = make_overlap_impl(timeout_ms=3000)
+    BM, BN, dur, algo = profile_gemm(impl, M, N, K, torch.float16, warmup=2, reps=5)
+    assert len(algo) == 5 and dur == sorted(dur) and all(d > 0 for d in dur)
+    cfg.save_stage1(M, N, K, BM, BN, dur, algo, tmp_path)
+
+    tiles = (M // BM[0]) * (N // BN[0])
+    ok, hint = compute_hint(impl, M, N, K, BM[0], BN[0], algo[0], 148 // (BM[0] // 128), "all_reduce",
+                            warmup=2, samples=6)
+    assert ok and sorted(hint) == list(range(tiles))
+
+    curve = torch.tensor([[2.0 ** 20, 200.0], [2.0 ** 26, 400.0]])
+    cfg.save_bandwidth(curve, "all_reduce", 1, path=tmp_path)
+    sol = search.predictive_search(impl, M, N, K, "all_reduce", cfg.load_bandwidth("all_reduce", 1, path=tmp_path),
+                                   path=tmp_path, reps=5, verbose=False)
+    data = cfg.load_config(M, N, K, tmp_path)
+    cfg.validate_stage2(data, M, N)
+    assert data["Algo"] == sol["Algo"] and data["search"] == "predictive" and data["fused_dur"] > 0
+
+    # the tuned file drives the reference-compatible layer + reorder-aware RMSNorm
+    layer = OverlapRowParallelLayer(0, 1, K, N, M, data, "all_reduce", [0] * 16)
+    norm = ReorderRMSNorm(N, M, data["BM"], data["BN"], data["hint"], eps=1e-5)
+    with torch.no_grad():
+        layer.weight.normal_(0.0, 1.0 / K ** 0.5)
+        norm.weight.fill_(1.0)
+        x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+        y = norm(layer(x))
+    torch.cuda.synchronize()
+    layer.overlap_class.check_status()
+    ref = x.float() @ layer.weight.float().t()
+    ref = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-5)
+    assert (y.float() - ref).abs().max().item() < 2e-2
+    impl.check_status()
