@@ -129,6 +129,8 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("nvls_available", &OverlapImpl::NvlsAvailable)
       .def("p2p_push", &OverlapImpl::P2pPush)
       .def("wait_on_unset_counter", &OverlapImpl::WaitOnUnsetCounter)
+      .def("set_transport", &OverlapImpl::SetTransport)
+      .def("transport", &OverlapImpl::Transport)
       .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)

@@ -4,7 +4,11 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <cuda.h>
+#include <unistd.h>
 
+#include <functional>
+
+#include "../kernels/rmsnorm.h"
 #include "checks.h"
 
 namespace fo {
@@ -93,6 +97,15 @@ GemmOperands OverlapImpl::operands(const at::Tensor& A, const at::Tensor& B, int
 
 void OverlapImpl::NcclInit(int64_t rank, int64_t size, std::vector<int64_t> id) {
   comm_.init(static_cast<int>(rank), static_cast<int>(size), id);
+  // Ranks on different hosts cannot map each other's memory: keep them on NCCL.
+  if (size > 1) {
+    char host[256] = {};
+    gethostname(host, sizeof(host) - 1);
+    const uint64_t mine = std::hash<std::string>{}(std::string(host));
+    std::vector<uint64_t> all(static_cast<size_t>(size));
+    comm_.all_gather_host(&mine, sizeof(mine), all.data());
+    for (uint64_t h : all) nccl_transport_ = nccl_transport_ || h != mine;
+  }
   const Communicator* c = &comm_;
   engine_.init(static_cast<int>(rank), static_cast<int>(size),
                [c](const void* send, size_t bytes, void* recv) { c->all_gather_host(send, bytes, recv); });
@@ -134,6 +147,10 @@ void OverlapImpl::GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C,
   OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
   const int64_t tiles = RA.numel();
   check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), if_monitor);
+  if (nccl_transport_) {
+    two_stream(false, A, B, C, nullptr, MM, RA, nullptr, rLDN, cSEG_CPU, cSEG_GPU, algo, 0, if_monitor);
+    return;
+  }
   cudaStream_t stream = current_stream();
   SignalArgs sig;
   if (if_monitor) {
@@ -165,6 +182,10 @@ void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tenso
   check_matrix(D, "D");
   TORCH_CHECK(D.scalar_type() == A.scalar_type() && D.numel() == static_cast<int64_t>(g.M) * g.N / ws,
               "D must hold M*N/size elements of A's dtype");
+  if (nccl_transport_) {
+    two_stream(true, A, B, C, &D, MM, RA, &RE, rLDN, cSEG_CPU, cSEG_GPU, algo, 0, if_monitor);
+    return;
+  }
   cudaStream_t stream = current_stream();
   SignalArgs sig;
   if (if_monitor) {
@@ -331,14 +352,14 @@ StreamWaitFn stream_wait_value32() {
 
 void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Tensor& C, at::Tensor* D, at::Tensor& MM,
                              at::Tensor& RA, at::Tensor* RE, int64_t rLDN, at::Tensor& cSEG_CPU, at::Tensor& cSEG_GPU,
-                             int64_t algo, int64_t gemm_ctas) {
+                             int64_t algo, int64_t gemm_ctas, bool monitor) {
   check_gemm_args(A, B, &C);
   require_comm("two-stream overlap");
   c10::cuda::CUDAGuard guard(A.device());
   GemmOperands g = operands(A, B, algo);
   OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
   const int64_t tiles = RA.numel();
-  check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), false);
+  check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), monitor);
   const int ws = comm_.world();
   const TileConfig tc = algo_config(g.algo);
   if (scatter) {
@@ -373,6 +394,10 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
   sig.cseg = cSEG_GPU.data_ptr<int>();
   sig.nseg = static_cast<int>(cSEG_GPU.numel());
   sig.slot_of_tile = RA.data_ptr<int>();
+  if (monitor) {  // completion tickets in the reference's MM layout
+    sig.ticket_counter = MM.data_ptr<int>() + (RA.size(1) - 1);
+    sig.trace = MM.data_ptr<int>() + RA.size(1);
+  }
   int ctas = static_cast<int>(gemm_ctas);
   if (ctas <= 0) ctas = device_sm_count() - 16;
   if (tc.ctas == 2) ctas &= ~1;
@@ -419,13 +444,13 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
 void OverlapImpl::GemmAllReduceTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA,
                                          int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo,
                                          int64_t gemm_ctas) {
-  two_stream(false, A, B, C, nullptr, MM, RA, nullptr, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas);
+  two_stream(false, A, B, C, nullptr, MM, RA, nullptr, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas, false);
 }
 
 void OverlapImpl::GemmReduceScatterTwoStream(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, at::Tensor MM,
                                              at::Tensor RA, at::Tensor RE, int64_t rLDN, at::Tensor cSEG_CPU,
                                              at::Tensor cSEG_GPU, int64_t algo, int64_t gemm_ctas) {
-  two_stream(true, A, B, C, &D, MM, RA, &RE, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas);
+  two_stream(true, A, B, C, &D, MM, RA, &RE, rLDN, cSEG_CPU, cSEG_GPU, algo, gemm_ctas, false);
 }
 
 at::Tensor OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, c10::optional<at::Tensor> weight, double eps,
@@ -442,6 +467,18 @@ at::Tensor OverlapImpl::GemmAllReduceFused(at::Tensor A, at::Tensor B, c10::opti
                 "weight must be a contiguous CUDA tensor of N values with A's dtype");
     norm.gamma = weight->data_ptr();
     norm.eps = static_cast<float>(eps);
+  }
+  if (nccl_transport_) {
+    cudaStream_t stream = current_stream();
+    at::Tensor C = torch::empty({g.M, g.N}, A.options());
+    engine_.gemm(g, C.data_ptr(), nullptr, nullptr, stream);
+    FO_NCCL_CHECK(ncclAllReduce(C.data_ptr(), C.data_ptr(), C.numel(), nccl_type(C), ncclSum, comm_.get(), stream));
+    if (norm.gamma != nullptr) {
+      at::Tensor O = torch::empty_like(C);
+      FO_CUDA_CHECK(launch_rmsnorm(C.data_ptr(), O.data_ptr(), norm.gamma, g.M, g.N, norm.eps, g.dtype, stream));
+      return O;
+    }
+    return C;
   }
   void* res = engine_.gemm_allreduce(g, nullptr, norm, nullptr, nullptr, current_stream());
   return torch::from_blob(res, {g.M, g.N}, A.options());
@@ -466,6 +503,20 @@ void OverlapImpl::GemmReduceScatterFused(at::Tensor A, at::Tensor B, at::Tensor 
     norm.gamma = weight->data_ptr();
     norm.eps = static_cast<float>(eps);
   }
+  if (nccl_transport_) {
+    TORCH_CHECK(!interleave, "interleaved row ownership needs the peer-to-peer transport");
+    cudaStream_t stream = current_stream();
+    at::Tensor C = torch::empty({g.M, g.N}, A.options());
+    engine_.gemm(g, C.data_ptr(), nullptr, nullptr, stream);
+    if (norm.gamma != nullptr) {
+      at::Tensor R = torch::empty_like(D);
+      FO_NCCL_CHECK(ncclReduceScatter(C.data_ptr(), R.data_ptr(), R.numel(), nccl_type(C), ncclSum, comm_.get(), stream));
+      FO_CUDA_CHECK(launch_rmsnorm(R.data_ptr(), D.data_ptr(), norm.gamma, g.M / ws, g.N, norm.eps, g.dtype, stream));
+    } else {
+      FO_NCCL_CHECK(ncclReduceScatter(C.data_ptr(), D.data_ptr(), D.numel(), nccl_type(C), ncclSum, comm_.get(), stream));
+    }
+    return;
+  }
   engine_.gemm_reducescatter(g, D.data_ptr(), interleave, norm, nullptr, nullptr, current_stream());
 }
 
@@ -482,6 +533,14 @@ void OverlapImpl::AllGatherGemm(at::Tensor A_shard, at::Tensor B, at::Tensor C, 
               " == 0, K % 8 == 0 (M = ", M, ", N = ", N, ", K = ", K, ")");
   check_matrix(C, "C");
   TORCH_CHECK(C.scalar_type() == A_shard.scalar_type() && C.size(0) == M && C.size(1) == N, "C must be [M, N]");
+  if (nccl_transport_) {
+    cudaStream_t stream = current_stream();
+    at::Tensor full = torch::empty({M, K}, A_shard.options());
+    FO_NCCL_CHECK(ncclAllGather(A_shard.data_ptr(), full.data_ptr(), A_shard.numel(), nccl_type(A_shard), comm_.get(),
+                                stream));
+    engine_.gemm(operands(full, B, algo), C.data_ptr(), nullptr, nullptr, stream);
+    return;
+  }
   engine_.allgather_gemm(A_shard.data_ptr(), B.data_ptr(), C.data_ptr(), static_cast<int>(M), static_cast<int>(N),
                          static_cast<int>(K), dtype_of(A_shard), static_cast<int>(algo), current_stream());
 }
@@ -498,6 +557,7 @@ void OverlapImpl::A2aDispatchGemm(at::Tensor A_send, at::Tensor B, at::Tensor C,
   check_gemm_args(A_send, B, nullptr);
   require_comm("a2a_dispatch_gemm");
   TORCH_CHECK(engine_ready_, "a2a_dispatch_gemm: call nccl_init first");
+  TORCH_CHECK(!nccl_transport_, "a2a_dispatch_gemm needs the peer-to-peer transport (all ranks on one node)");
   const int ws = comm_.world(), rank = comm_.rank();
   const int64_t m_pad = A2aPaddedRows(mLen_CPU, algo);
   const int* len = mLen_CPU.data_ptr<int>();
@@ -555,6 +615,12 @@ void OverlapImpl::WaitOnUnsetCounter(int64_t timeout_ms) {
   TORCH_CHECK(timeout_ms > 0 && timeout_ms <= 5000, "timeout must be in (0, 5000] ms");
   engine_.wait_on_unset_counter(timeout_ms, current_stream());
 }
+
+void OverlapImpl::SetTransport(std::string name) {
+  TORCH_CHECK(name == "p2p" || name == "nccl", "transport must be \"p2p\" or \"nccl\"");
+  nccl_transport_ = name == "nccl" && comm_.world() > 1;
+}
+std::string OverlapImpl::Transport() { return nccl_transport_ ? "nccl" : "p2p"; }
 
 void OverlapImpl::SetTimeoutMs(int64_t ms) {
   TORCH_CHECK(ms > 0, "timeout must be positive");

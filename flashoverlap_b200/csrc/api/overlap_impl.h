@@ -87,6 +87,16 @@ class OverlapImpl : public torch::CustomClassHolder {
   // (bandwidth tool); `ctas` = 0 uses every SM.
   void P2pPush(int64_t bytes, int64_t ctas);
 
+  // ---- transport ---------------------------------------------------------
+  // "p2p" (default on one node): the fused kernels move data through
+  // peer-mapped memory.  "nccl": ranks that cannot map each other's memory
+  // (several nodes) keep every entry point working on NCCL: the overlap calls
+  // run the two-stream design, the fused calls run GEMM, one NCCL collective and
+  // the RMSNorm kernel.  nccl_init selects "nccl" by itself when the ranks sit
+  // on different hosts.
+  void SetTransport(std::string name);
+  std::string Transport();
+
   // ---- tuning knobs and failure reporting ---------------------------------
   // Failure-path self test, see FusedEngine::wait_on_unset_counter.
   void WaitOnUnsetCounter(int64_t timeout_ms);
@@ -112,12 +122,13 @@ class OverlapImpl : public torch::CustomClassHolder {
 
   void two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Tensor& C, at::Tensor* D, at::Tensor& MM,
                   at::Tensor& RA, at::Tensor* RE, int64_t rLDN, at::Tensor& cSEG_CPU, at::Tensor& cSEG_GPU,
-                  int64_t algo, int64_t gemm_ctas);
+                  int64_t algo, int64_t gemm_ctas, bool monitor);
   Communicator comm_;
   FusedEngine engine_;
   cudaStream_t comm_stream_ = nullptr;
   cudaEvent_t join_event_ = nullptr;
   const void* checked_row_map_ = nullptr;
+  bool nccl_transport_ = false;
   bool engine_ready_ = false;
   at::Tensor phase_trace_;
 };

@@ -207,6 +207,31 @@ def main():
         print(f"{'PASS' if ok else 'FAIL'} two-stream comparator leaves the counters at zero", flush=True)
     failures += 0 if ok else 1
 
+    # NCCL transport (what ranks on different nodes fall back to), forced here on one node
+    assert impl.transport() == "p2p"
+    impl.set_transport("nccl")
+    out = impl.gemm_allreduce_fused(A, B, W, 1e-5, algo)
+    torch.cuda.synchronize()
+    check("nccl transport: gemm_allreduce_fused + norm", out, rms_ref(ref, W, 1e-5), 1e-2)
+    rows = M // world
+    Dn = torch.full((rows, N), float("nan"), device=dev, dtype=torch.float16)
+    impl.gemm_reducescatter_fused(A, B, Dn, W, 1e-5, algo, False)
+    torch.cuda.synchronize()
+    check("nccl transport: gemm_reducescatter_fused + norm", Dn, rms_ref(ref[rank * rows:(rank + 1) * rows], W, 1e-5),
+          1e-2)
+    MM.zero_()
+    C = torch.full((M, N), float("nan"), device=dev, dtype=torch.float16)
+    impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, False)
+    torch.cuda.synchronize()
+    check("nccl transport: gemm_allreduce_overlap", from_tile_order(C, bm, bn, RA), ref, 1e-2)
+    g5 = torch.Generator(device="cpu").manual_seed(31337)
+    A_full = torch.randn(M, K, generator=g5).to(dev, torch.float16)
+    Cg = torch.empty((M, N), device=dev, dtype=torch.float16)
+    impl.allgather_gemm(A_full[rank * rows:(rank + 1) * rows].contiguous(), B, Cg, algo)
+    torch.cuda.synchronize()
+    check("nccl transport: allgather_gemm", Cg, A_full.float() @ B.float().t(), 1e-2)
+    impl.set_transport("p2p")
+
     # non-overlapped paths and the cuBLAS + NCCL baseline
     base = make_baseline_impl()
     C1 = torch.empty((M, N), device=dev, dtype=torch.float16)
