@@ -4,6 +4,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <cuda.h>
+#include <nvtx3/nvToolsExt.h>
 #include <unistd.h>
 
 #include <functional>
@@ -353,6 +354,10 @@ StreamWaitFn stream_wait_value32() {
 void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Tensor& C, at::Tensor* D, at::Tensor& MM,
                              at::Tensor& RA, at::Tensor* RE, int64_t rLDN, at::Tensor& cSEG_CPU, at::Tensor& cSEG_GPU,
                              int64_t algo, int64_t gemm_ctas, bool monitor) {
+  nvtxRangePushA(scatter ? "flashoverlap::two_stream_reducescatter" : "flashoverlap::two_stream_allreduce");
+  struct Pop {
+    ~Pop() { nvtxRangePop(); }
+  } pop;
   check_gemm_args(A, B, &C);
   require_comm("two-stream overlap");
   c10::cuda::CUDAGuard guard(A.device());
