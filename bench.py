@@ -8,15 +8,23 @@ sm_100a kernel per step.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
 
-Rank 0 prints one JSON line.  ``value`` is the aggregate rate of the whole job
-(2*M*N*K_total FLOP per step over the slowest rank's device time), measured with
-CUDA events around every step with an L2 flush before each; ``e2e`` is the same
-step through ``FusedRowParallelLinear.forward`` including the host-to-device
-copy of the step's activations and the device-to-host read of a result row.
-The same run also times the non-overlapped path the reference calls its
-baseline (vendor GEMM, then one NCCL collective, then RMSNorm; reference:
-src/baseline_impl.cu:35-70) and a second shape (reduce-scatter, bf16) and
-reports them in ``detail``.
+Rank 0 prints one JSON line.
+
+* ``value`` / ``ms_per_step``: the fused kernel alone, CUDA events around every
+  step with an L2 flush before each, slowest rank; ``value`` is the aggregate
+  rate of the whole job (2*M*N*K_total FLOP per step).
+* ``vs_baseline``: speed-up over the non-overlapped path the reference calls its
+  baseline (vendor GEMM, one NCCL collective on the same stream, RMSNorm kernel;
+  reference: src/baseline_impl.cu:35-70), measured in alternation with the
+  fused step in the same process.
+* ``e2e``: the same step through ``FusedRowParallelLinear.forward`` including,
+  every step, the host-to-device copy of the step's activations from pinned
+  memory and the device-to-host copy of the WHOLE result.
+* ``detail``: the baseline, the reference's two-stream overlap design with a
+  searched wave grouping, the second named shape (GEMM + ReduceScatter + RMSNorm
+  in bf16), all-gather->GEMM and all-to-all->GEMM timings, and numerical checks
+  of every fused operation against fp32 PyTorch and against the NCCL baseline.
+  A failed check makes the process exit non-zero.
 
 ``--impl reference`` reports that the reference cannot run here.
 """
@@ -25,6 +33,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import sys
 import time
 
@@ -41,8 +50,12 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", type=int, default=3, help="tile configuration (3 = 256x256 CTA pair)")
-    ap.add_argument("--no-detail", action="store_true", help="skip the baseline and the second shape")
+    ap.add_argument("--no-detail", action="store_true", help="skip the baseline, the checks and the other shapes")
     return ap.parse_args()
+
+
+def stats(ts):
+    return {"min": round(min(ts), 4), "median": round(statistics.median(ts), 4), "max": round(max(ts), 4)}
 
 
 def main():
@@ -59,7 +72,9 @@ def main():
     import flashoverlap_b200  # noqa: F401
     from flashoverlap_b200.models import FusedRowParallelLinear
     from flashoverlap_b200.parallel import init_distributed, make_baseline_impl, make_overlap_impl, max_over_ranks
+    from flashoverlap_b200.tune.runtime import search_two_stream
     from flashoverlap_b200.utils.clocks import ClockSampler
+    from flashoverlap_b200.utils.pipeline import HostFeeder, ResultReader
     from flashoverlap_b200.utils.timing import time_pairs, time_steps
 
     if not torch.cuda.is_available():
@@ -86,105 +101,83 @@ def main():
         layer.norm_weight.copy_((1 + 0.1 * torch.randn(N, device=dev)).to(dtype))
     x_host = (torch.randn(M, K) / K ** 0.5).to(dtype).pin_memory()
     x = x_host.to(dev)
-    row_host = torch.empty(N, dtype=dtype).pin_memory()
 
     def step():
         layer(x)
 
+    def mx(ts):
+        """Per-step times of the slowest rank: element-wise maximum over the ranks."""
+        if world == 1:
+            return list(ts)
+        t = torch.tensor(ts, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
     # ---- device-timed steps ---------------------------------------------------
     with ClockSampler(torch.cuda.current_device()) as sampler:
-        times = time_steps(step, steps, warmup, flush=True)
+        times = mx(time_steps(step, steps, warmup, flush=True))
     clocks = sampler.summary()
     impl.check_status()
-    total_ms = max_over_ranks(sum(times))
-    ms_per_step = total_ms / steps
+    ms_per_step = sum(times) / steps
     flop = 2.0 * M * N * K_total
     value = flop / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public API -------------------------------------
-    # Every step copies its activations from pinned host memory and reads a row of
-    # the result back.  The copy of step i+1 runs on a copy stream while step i
-    # computes (HostFeeder); every timed step still issues exactly one H2D copy
-    # and one D2H read inside the timed region.
-    from flashoverlap_b200.utils.pipeline import HostFeeder
-
+    # Every step copies its activations from pinned host memory and copies the
+    # whole result back into pinned host memory.  Both copies are double
+    # buffered (the input of step i+1 and the result of step i-1 travel while
+    # step i computes), and every timed step issues exactly one of each inside
+    # the timed region; the last result is waited for before the clock stops.
     feeder = HostFeeder((M, K), dtype, dev)
+    reader = ResultReader((M, N), dtype, dev)
     feeder.submit(x_host)
 
     def e2e_step():
         xd = feeder.take()
         feeder.submit(x_host)          # next step's input starts travelling now
+        reader.before_step()           # the result buffer of two steps ago has been read out
         out = layer(xd)
         feeder.release(xd)
-        row_host.copy_(out[0], non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the result row has arrived on the host
+        reader.fetch(out)              # device -> pinned host on the copy stream, once the kernel is done
 
     for _ in range(warmup):
         e2e_step()
+    reader.wait_all()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(steps):
         e2e_step()
+    reader.wait_all()                  # the last result has arrived on the host
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / steps
     if world > 1:
         dist.barrier()
     impl.check_status()
     e2e_value = flop / (e2e_ms * 1e-3) / 1e12
+    # the parts, each alone (device time, this rank): input copy, kernel, result copy
+    dst = torch.empty(M, K, dtype=dtype, device=dev)
+    res = layer(x)
+    host_out = torch.empty(M, N, dtype=dtype).pin_memory()
+    h2d_ms = statistics.median(time_steps(lambda: dst.copy_(x_host, non_blocking=True), 5, 2, flush=False,
+                                          barrier=False))
+    d2h_ms = statistics.median(time_steps(lambda: host_out.copy_(res, non_blocking=True), 5, 2, flush=False,
+                                          barrier=False))
 
-    detail = {}
+    detail = {"per_step_ms": stats(times)}
+    vs_baseline = None
+    ok = True
     if not args.no_detail:
-        # non-overlapped baseline: cuBLAS GEMM, NCCL all-reduce, RMSNorm kernel
-        base = make_baseline_impl()
-        C = torch.empty(M, N, device=dev, dtype=dtype)
-        O = torch.empty(M, N, device=dev, dtype=dtype)
+        from bench_detail import run_detail  # beside this file
 
-        def base_step():
-            base.gemm_allreduce(x, layer.weight, C)
-            torch.ops.flashoverlap_op.rmsnorm(C, O, layer.norm_weight, eps)
-
-        # fused and baseline steps alternate so that both see the same clocks
-        ft, bt = time_pairs(step, base_step, steps, warmup)
-        fused_ms2 = max_over_ranks(sum(ft)) / steps
-        base_ms = max_over_ranks(sum(bt)) / steps
-        gt, ct = time_pairs(lambda: impl.cutlass_gemm(x, layer.weight, C, args.algo),
-                            lambda: base.cublas_gemm(x, layer.weight, C), steps, warmup)
-        gemm_ms = max_over_ranks(sum(gt)) / steps
-        cublas_ms = max_over_ranks(sum(ct)) / steps
-        detail["ar_fp16"] = {
-            "fused_ms": round(fused_ms2, 4), "nccl_baseline_ms": round(base_ms, 4),
-            "speedup_vs_nccl_baseline": round(base_ms / fused_ms2, 3), "measured": "alternating steps",
-            "own_gemm_ms": round(gemm_ms, 4), "cublas_gemm_ms": round(cublas_ms, 4),
-        }
-        # second shape: MLP down-projection, GEMM + ReduceScatter + RMSNorm, bf16
-        M2, N2, K2_total = 8192, 8192, 28672
-        K2 = K2_total // world
-        A2 = (torch.randn(M2, K2, device=dev) / K2 ** 0.5).to(torch.bfloat16)
-        B2 = (torch.randn(N2, K2, device=dev) / K2 ** 0.5).to(torch.bfloat16)
-        W2 = (1 + 0.1 * torch.randn(N2, device=dev)).to(torch.bfloat16)
-        D2 = torch.empty(M2 // world, N2, device=dev, dtype=torch.bfloat16)
-        C2 = torch.empty(M2, N2, device=dev, dtype=torch.bfloat16)
-        O2 = torch.empty_like(D2)
-        def base_rs():
-            base.gemm_reducescatter(A2, B2, C2, D2)
-            torch.ops.flashoverlap_op.rmsnorm(D2, O2, W2, eps)
-
-        rt, brt = time_pairs(lambda: impl.gemm_reducescatter_fused(A2, B2, O2, W2, eps, args.algo, False), base_rs,
-                             steps, warmup)
-        rs_ms = max_over_ranks(sum(rt)) / steps
-        base_rs_ms = max_over_ranks(sum(brt)) / steps
-        detail["rs_bf16"] = {
-            "M": M2, "N": N2, "K_per_rank": K2, "fused_ms": round(rs_ms, 4), "nccl_baseline_ms": round(base_rs_ms, 4),
-            "speedup_vs_nccl_baseline": round(base_rs_ms / rs_ms, 3),
-            "tflops": round(2.0 * M2 * N2 * K2_total / (rs_ms * 1e-3) / 1e12, 1),
-        }
-        impl.check_status()
+        detail_more, vs_baseline, ok = run_detail(impl, layer, x, steps, warmup, args.algo, mx, stats)
+        detail.update(detail_more)
 
     if rank == 0:
         line = {
-            "metric": "fused GEMM+AllReduce+RMSNorm throughput (aggregate TFLOP/s; latency in ms_per_step)",
+            "metric": "fused GEMM+AllReduce+RMSNorm: aggregate TFLOP/s (value), latency (ms_per_step) and speed-up "
+                      "over the non-overlapped cuBLAS+NCCL+RMSNorm path (vs_baseline)",
             "value": round(value, 2),
             "unit": "TFLOP/s",
             "n_gpus": world,
@@ -193,7 +186,7 @@ def main():
             "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": True,
             "scaling": "strong",
-            "vs_baseline": None,
+            "vs_baseline": vs_baseline,
             "dtype": "fp16",
             "data": "synthetic (random-init weights and activations ~ N(0,1)/sqrt(K))",
             "config": {
@@ -203,15 +196,21 @@ def main():
                 "l2": "flushed between timed iterations (256 MB write)",
                 "timing": "CUDA events per step, max over ranks",
                 "algo": args.algo,
+                "transport": "NVLS multimem" if impl.nvls_available() else "P2P stores",
+                "vs_baseline_is": "nccl_baseline_ms / fused_ms, alternating steps (no published B200 number exists)",
             },
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "power_w_max": clocks["power_w_max"], "samples": clocks["samples"],
                        "samples_under_load": clocks["samples_under_load"]},
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 5),
                     "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": row_host.numel() * row_host.element_size(),
-                    "api": "HostFeeder + FusedRowParallelLinear.forward", "timing": "wall clock, max over ranks",
-                    "note": "H2D of the next step overlaps the current step (double-buffered)"},
+                    "d2h_bytes_per_step": M * N * 2,
+                    "breakdown_ms": {"h2d_alone": round(h2d_ms, 4), "kernel_alone": round(ms_per_step, 4),
+                                     "d2h_alone": round(d2h_ms, 4)},
+                    "api": "HostFeeder + FusedRowParallelLinear.forward + ResultReader",
+                    "timing": "wall clock, max over ranks",
+                    "note": "both copies are double-buffered: the input of step i+1 and the result of step i-1 "
+                            "travel while step i computes; the whole [M, N] result is copied every step"},
             "gpu_launches": steps,
             "impl": "ours",
             "detail": detail,
@@ -220,7 +219,7 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return 0 if ok else 1
 
 
 if __name__ == "__main__":

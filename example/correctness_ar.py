@@ -8,7 +8,14 @@ example/correctness_ar.py:99-127; tolerance 1e-2), plus the natively fused layer
 import argparse
 
 import torch.distributed as dist
-from _common import finish, make_overlap_impl, start, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import finish, make_overlap_impl, start  # noqa: E402
 
 from flashoverlap_b200.models import FusedRowParallelLinear, OverlapRowParallelLayer, ReorderRMSNorm, RMSNorm, \
     RowParallelLayer

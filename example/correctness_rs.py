@@ -9,7 +9,14 @@ path feeds the same rows grouped by ``row % size`` to reduce_scatter_tensor.
 import argparse
 
 import torch.distributed as dist
-from _common import finish, make_overlap_impl, start, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import finish, make_overlap_impl, start  # noqa: E402
 from correctness_ar import default_config
 
 from flashoverlap_b200.models import FusedRowParallelLinear, OverlapRowParallelLayer, ReorderRMSNorm, RMSNorm, \

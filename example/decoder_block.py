@@ -6,7 +6,14 @@
 import argparse
 
 import torch.distributed as dist
-from _common import DTYPES, finish, make_overlap_impl, start, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES, finish, make_overlap_impl, start  # noqa: E402
 
 from flashoverlap_b200.models.decoder_block import TPDecoderBlock
 from flashoverlap_b200.parallel import max_over_ranks

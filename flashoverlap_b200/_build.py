@@ -48,12 +48,15 @@ def library_path() -> Path:
 
 
 def _existing_sources() -> list[Path]:
-    return [(_CSRC / s) for s in SOURCES if (_CSRC / s).exists()]
+    """The fixed sources plus one generated file per kernel instance
+    (tool/generate_instances.py writes csrc/kernels/generated/)."""
+    generated = sorted((_CSRC / "kernels" / "generated").glob("*.cu"))
+    return [(_CSRC / s) for s in SOURCES if (_CSRC / s).exists()] + generated
 
 
 def _source_digest() -> str:
     h = hashlib.sha256()
-    files = sorted(p for p in _CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h"})
+    files = sorted(p for p in _CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h", ".inc"})
     for p in files:
         h.update(str(p.relative_to(_CSRC)).encode())
         h.update(p.read_bytes())
@@ -114,7 +117,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     )
     if not _LIB.exists():
         raise RuntimeError(f"flashoverlap_b200: build finished but {_LIB} is missing")
-    newest = max(p.stat().st_mtime for p in _CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h"})
+    newest = max(p.stat().st_mtime for p in _CSRC.rglob("*") if p.suffix in {".cu", ".cuh", ".cpp", ".h", ".inc"})
     if _LIB.stat().st_mtime < newest:
         # (a retry after a failed build in the same process makes torch skip the build and load the old file)
         raise RuntimeError(f"flashoverlap_b200: {_LIB} is older than its sources: the build did not replace it; "

@@ -5,6 +5,8 @@
 // either run unchanged.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <mutex>
+
 #include <torch/custom_class.h>
 #include <torch/library.h>
 
@@ -35,6 +37,12 @@ static void reorder_rmsnorm_eps(at::Tensor X, at::Tensor RX, at::Tensor RW, int6
   const int64_t tiles = (bs / BM) * (dim / BN);
   TORCH_CHECK(RA.numel() == tiles, "RA must have ", tiles, " entries, got ", RA.numel());
   TORCH_CHECK(rldn >= 1 && tiles % rldn == 0, "rldn must divide the number of tiles");
+  {  // the kernel gathers through RA: an entry outside [0, tiles) would read outside X
+    static std::mutex mu;
+    static IndexCheckCache checked;
+    std::lock_guard<std::mutex> lock(mu);
+    checked.require_permutation(RA, tiles, "RA");
+  }
   OutLayout L{};
   L.tiled = 1;
   L.bm = static_cast<int>(BM);
@@ -125,9 +133,12 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("a2a_dispatch_gemm", &OverlapImpl::A2aDispatchGemm)
       .def("a2a_padded_rows", &OverlapImpl::A2aPaddedRows)
       .def("attach_symmetric", &OverlapImpl::AttachSymmetric)
+      .def("detach_symmetric", &OverlapImpl::DetachSymmetric)
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)
       .def("p2p_push", &OverlapImpl::P2pPush)
+      .def("p2p_push_bulk", &OverlapImpl::P2pPushBulk)
+      .def("multimem_bench", &OverlapImpl::MultimemBench)
       .def("wait_on_unset_counter", &OverlapImpl::WaitOnUnsetCounter)
       .def("set_transport", &OverlapImpl::SetTransport)
       .def("transport", &OverlapImpl::Transport)
@@ -135,7 +146,6 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)
       .def("set_phase_trace", &OverlapImpl::SetPhaseTrace)
-      .def("set_reduce_group", &OverlapImpl::SetReduceGroup)
       .def("status", &OverlapImpl::Status)
       .def("status_string", &OverlapImpl::StatusString)
       .def("check_status", &OverlapImpl::CheckStatus)

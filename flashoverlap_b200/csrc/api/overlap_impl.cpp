@@ -9,6 +9,7 @@
 
 #include <functional>
 
+#include "../kernels/comm_kernels.h"
 #include "../kernels/rmsnorm.h"
 #include "checks.h"
 
@@ -22,7 +23,8 @@ cudaStream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream()
 
 // Validates the reference's reorder/segment arguments and returns the layout
 // they describe for an M x N matrix (tile shape from RA's 2-D shape).
-OutLayout tiled_layout(int64_t M, int64_t N, const at::Tensor& RA, int64_t rLDN, int64_t algo) {
+OutLayout tiled_layout(int64_t M, int64_t N, const at::Tensor& RA, int64_t rLDN, int64_t algo,
+                       IndexCheckCache& checked) {
   check_int_tensor(RA, "RA", true);
   TORCH_CHECK(RA.dim() == 2, "RA must be 2-D [M/BM, N/BN]");
   const int64_t tm = RA.size(0), tn = RA.size(1);
@@ -31,6 +33,7 @@ OutLayout tiled_layout(int64_t M, int64_t N, const at::Tensor& RA, int64_t rLDN,
   TORCH_CHECK(M / tm == tc.bm && N / tn == tc.bn, "RA describes ", M / tm, "x", N / tn, " tiles but Algo ", algo,
               " computes ", tc.bm, "x", tc.bn, " tiles");
   TORCH_CHECK(rLDN >= 1 && (tm * tn) % rLDN == 0, "rLDN must divide the number of tiles");
+  checked.require_permutation(RA, tm * tn, "RA");  // the kernels store through RA
   OutLayout L{};
   L.tiled = 1;
   L.bm = tc.bm;
@@ -71,6 +74,7 @@ void check_segments(const at::Tensor& cSEG_CPU, const at::Tensor& cSEG_GPU, int6
 OverlapImpl::OverlapImpl() = default;
 OverlapImpl::~OverlapImpl() {
   if (join_event_ != nullptr) cudaEventDestroy(join_event_);
+  if (raise_event_ != nullptr) cudaEventDestroy(raise_event_);
   if (comm_stream_ != nullptr) cudaStreamDestroy(comm_stream_);
 }
 
@@ -145,7 +149,7 @@ void OverlapImpl::GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C,
   require_comm("gemm_allreduce_overlap");
   c10::cuda::CUDAGuard guard(A.device());
   GemmOperands g = operands(A, B, algo);
-  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
+  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo, index_checks_);
   const int64_t tiles = RA.numel();
   check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), if_monitor);
   if (nccl_transport_) {
@@ -173,12 +177,13 @@ void OverlapImpl::GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tenso
   c10::cuda::CUDAGuard guard(A.device());
   GemmOperands g = operands(A, B, algo);
   const int ws = comm_.world();
-  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
+  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo, index_checks_);
   const int64_t tiles = RA.numel();
   check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), if_monitor);
   check_int_tensor(RE, "RE", true);
   TORCH_CHECK(RE.numel() == static_cast<int64_t>(g.M) * g.N / L.bn, "RE must have M*N/BN = ",
               static_cast<int64_t>(g.M) * g.N / L.bn, " entries, got ", RE.numel());
+  index_checks_.require_range(RE, RE.numel(), "RE");
   TORCH_CHECK(L.bm % ws == 0, "BM must be divisible by the world size");
   check_matrix(D, "D");
   TORCH_CHECK(D.scalar_type() == A.scalar_type() && D.numel() == static_cast<int64_t>(g.M) * g.N / ws,
@@ -362,7 +367,7 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
   require_comm("two-stream overlap");
   c10::cuda::CUDAGuard guard(A.device());
   GemmOperands g = operands(A, B, algo);
-  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo);
+  OutLayout L = tiled_layout(g.M, g.N, RA, rLDN, algo, index_checks_);
   const int64_t tiles = RA.numel();
   check_segments(cSEG_CPU, cSEG_GPU, tiles, MM, RA.size(1), monitor);
   const int ws = comm_.world();
@@ -376,10 +381,7 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
     TORCH_CHECK(L.bm % ws == 0, "BM must be divisible by the world size");
     TORCH_CHECK(rLDN == 1, "the row map is defined for rLDN == 1");
     TORCH_CHECK(RE->numel() == static_cast<int64_t>(g.M) * g.N / L.bn, "RE must have M*N/BN entries");
-    if (RE->data_ptr() != checked_row_map_) {  // the epilogue stores through this map: check it once per tensor
-      TORCH_CHECK(RE->min().item<int>() >= 0 && RE->max().item<int>() < RE->numel(), "RE holds a row outside the buffer");
-      checked_row_map_ = RE->data_ptr();
-    }
+    index_checks_.require_range(*RE, RE->numel(), "RE");  // the epilogue stores through this map
   }
   auto wait_fn = stream_wait_value32();
   TORCH_CHECK(wait_fn != nullptr, "cuStreamWaitValue32 is not available from this driver");
@@ -388,6 +390,7 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
     FO_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     FO_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
     FO_CUDA_CHECK(cudaEventCreateWithFlags(&join_event_, cudaEventDisableTiming));
+    FO_CUDA_CHECK(cudaEventCreateWithFlags(&raise_event_, cudaEventDisableTiming));
   }
   cudaStream_t stream = current_stream();
   // the collectives may start only after earlier work on the caller's stream (inputs, previous use of C / MM)
@@ -408,6 +411,8 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
   if (tc.ctas == 2) ctas &= ~1;
   TORCH_CHECK(ctas >= tc.ctas, "too few CTAs for the GEMM");
   g.sm_count = ctas;
+  // the segment counters start from zero whatever an earlier (possibly aborted) call left in them
+  FO_CUDA_CHECK(cudaMemsetAsync(MM.data_ptr<int>(), 0, sizeof(int) * cSEG_CPU.numel(), stream));
   if (scatter) {
     // rows of every tile grouped by (row % size), segment by segment: what the
     // reference's scatter epilogue writes through its row map RE
@@ -417,6 +422,13 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
   } else {
     engine_.gemm(g, C.data_ptr(), &L, &sig, stream);
   }
+  // The stream waits below have no deadline of their own.  This kernel runs on
+  // the caller's stream right after the GEMM and raises every segment counter
+  // to its target, so the waits end when the GEMM has ended, also when the
+  // GEMM gave up on one of its bounded waits (its status word then says so).
+  FO_CUDA_CHECK(launch_raise_counters(MM.data_ptr<int>(), cSEG_GPU.data_ptr<int>(), tc.ctas,
+                                      static_cast<int>(cSEG_CPU.numel()), stream));
+  FO_CUDA_CHECK(cudaEventRecord(raise_event_, stream));
   const int* seg = cSEG_CPU.data_ptr<int>();
   const size_t tile_elems = static_cast<size_t>(L.bm) * L.bn;
   const size_t esz = C.element_size();
@@ -440,7 +452,8 @@ void OverlapImpl::two_stream(bool scatter, at::Tensor& A, at::Tensor& B, at::Ten
     }
     done += count;
   }
-  // the counters return to zero (the reference's wait kernel swaps them back on success)
+  // the counters return to zero (the reference's wait kernel swaps them back on success), after the raise
+  FO_CUDA_CHECK(cudaStreamWaitEvent(comm_stream_, raise_event_, 0));
   FO_CUDA_CHECK(cudaMemsetAsync(MM.data_ptr<int>(), 0, sizeof(int) * cSEG_CPU.numel(), comm_stream_));
   FO_CUDA_CHECK(cudaEventRecord(join_event_, comm_stream_));
   FO_CUDA_CHECK(cudaStreamWaitEvent(stream, join_event_, 0));
@@ -607,6 +620,10 @@ void OverlapImpl::AttachSymmetric(std::vector<int64_t> peer_ptrs, int64_t mc_ptr
   for (int64_t v : peer_ptrs) ptrs.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(v)));
   engine_.attach_symmetric(static_cast<size_t>(nbytes), ptrs, reinterpret_cast<void*>(static_cast<uintptr_t>(mc_ptr)));
 }
+void OverlapImpl::DetachSymmetric() {
+  TORCH_CHECK(engine_ready_, "detach_symmetric: call nccl_init first");
+  engine_.detach_symmetric();
+}
 void OverlapImpl::SetUseNvls(bool allreduce, bool reducescatter) { engine_.set_use_nvls(allreduce, reducescatter); }
 bool OverlapImpl::NvlsAvailable() { return engine_.nvls_available(); }
 
@@ -614,6 +631,23 @@ void OverlapImpl::P2pPush(int64_t bytes, int64_t ctas) {
   require_comm("p2p_push");
   TORCH_CHECK(engine_ready_, "p2p_push: call nccl_init first");
   engine_.p2p_push(bytes, static_cast<int>(ctas), current_stream());
+}
+
+void OverlapImpl::P2pPushBulk(int64_t bytes, int64_t chunk_bytes, int64_t ctas) {
+  require_comm("p2p_push_bulk");
+  TORCH_CHECK(engine_ready_, "p2p_push_bulk: call nccl_init first");
+  engine_.p2p_push_bulk(bytes, static_cast<int>(chunk_bytes), static_cast<int>(ctas), current_stream());
+}
+
+void OverlapImpl::MultimemBench(std::string kind, int64_t bytes, int64_t ctas, bool bf16) {
+  require_comm("multimem_bench");
+  TORCH_CHECK(engine_ready_, "multimem_bench: call nccl_init first");
+  int k = -1;
+  if (kind == "ld_reduce") k = MM_LD_REDUCE;
+  else if (kind == "st") k = MM_ST;
+  else if (kind == "allreduce") k = MM_ALLREDUCE;
+  TORCH_CHECK(k >= 0, "multimem_bench: kind must be ld_reduce, st or allreduce");
+  engine_.multimem_bench(k, bytes, static_cast<int>(ctas), bf16 ? DT_BF16 : DT_F16, current_stream());
 }
 
 void OverlapImpl::WaitOnUnsetCounter(int64_t timeout_ms) {
@@ -633,10 +667,6 @@ void OverlapImpl::SetTimeoutMs(int64_t ms) {
 }
 void OverlapImpl::SetSmCount(int64_t n) { engine_.set_sm_count(static_cast<int>(n)); }
 void OverlapImpl::SetRasterGroup(int64_t g) { engine_.set_raster_group(static_cast<int>(g)); }
-void OverlapImpl::SetReduceGroup(int64_t g) {
-  TORCH_CHECK(g == 0 || g == 1 || g == 2 || g == 4 || g == 8, "reduce group must be 0, 1, 2, 4 or 8");
-  engine_.set_reduce_group(static_cast<int>(g));
-}
 void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
   if (buf.numel() == 0) {
     engine_.set_phase_trace(nullptr);
@@ -644,7 +674,8 @@ void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
     return;
   }
   TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && buf.scalar_type() == at::kLong, "trace buffer must be a contiguous CUDA int64 tensor");
-  TORCH_CHECK(buf.numel() >= 4 * device_sm_count(), "trace buffer needs 4 entries per SM (", 4 * device_sm_count(), ")");
+  TORCH_CHECK(buf.numel() >= kTraceWords * device_sm_count(), "trace buffer needs ", kTraceWords, " entries per SM (",
+              kTraceWords * device_sm_count(), ")");
   phase_trace_ = buf;  // keeps the memory alive
   engine_.set_phase_trace(reinterpret_cast<unsigned long long*>(buf.data_ptr<int64_t>()));
 }

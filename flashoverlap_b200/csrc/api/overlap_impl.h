@@ -13,6 +13,7 @@
 #include <memory>
 
 #include "../runtime/engine.h"
+#include "checks.h"
 #include "nccl_utils.h"
 
 namespace fo {
@@ -29,6 +30,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   void Gemm(at::Tensor A, at::Tensor B, at::Tensor C, int64_t algo);
   void GemmAllReduceOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor MM, at::Tensor RA, int64_t rLDN,
                             at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo, bool if_monitor);
+  // (C is scratch: in the reference it holds this rank's partial products for
+  // NCCL to read; the fused kernel stages partials in symmetric memory instead
+  // and leaves C untouched.)
   void GemmReduceScatterOverlap(at::Tensor A, at::Tensor B, at::Tensor C, at::Tensor D, at::Tensor MM, at::Tensor RA,
                                 at::Tensor RE, int64_t rLDN, at::Tensor cSEG_CPU, at::Tensor cSEG_GPU, int64_t algo,
                                 bool if_monitor);
@@ -80,12 +84,19 @@ class OverlapImpl : public torch::CustomClassHolder {
   // multicast address (0 = none), `nbytes` the size of each buffer.  With a
   // multicast address the fused operations reduce through NVLink SHARP.
   void AttachSymmetric(std::vector<int64_t> peer_ptrs, int64_t mc_ptr, int64_t nbytes);
+  // Collective.  Drops the attached memory again (used when some rank could not map it).
+  void DetachSymmetric();
   void SetUseNvls(bool allreduce, bool reducescatter);
   bool NvlsAvailable();
 
   // Collective: all-to-all push of `bytes` per peer with the P2P store kernel
   // (bandwidth tool); `ctas` = 0 uses every SM.
   void P2pPush(int64_t bytes, int64_t ctas);
+  // Same with bulk copies from shared memory, `chunk_bytes` per copy.
+  void P2pPushBulk(int64_t bytes, int64_t chunk_bytes, int64_t ctas);
+  // Collective NVLink SHARP primitive over `bytes` of symmetric memory:
+  // kind "ld_reduce" | "st" | "allreduce"; each rank handles its 1/size share.
+  void MultimemBench(std::string kind, int64_t bytes, int64_t ctas, bool bf16);
 
   // ---- transport ---------------------------------------------------------
   // "p2p" (default on one node): the fused kernels move data through
@@ -103,9 +114,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   void SetTimeoutMs(int64_t ms);
   void SetSmCount(int64_t n);
   void SetRasterGroup(int64_t g);
-  void SetReduceGroup(int64_t g);
   // Every following launch records per-CTA phase timestamps into `buf`
-  // (int64, at least 4 * SM count entries; an empty tensor turns it off).
+  // (int64, at least 8 * SM count entries, layout in FusedParams::phase_trace;
+  // an empty tensor turns it off).
   void SetPhaseTrace(at::Tensor buf);
   // [code, rank, where, seen, want]; code 0 = no failure reported.
   std::vector<int64_t> Status();
@@ -127,7 +138,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   FusedEngine engine_;
   cudaStream_t comm_stream_ = nullptr;
   cudaEvent_t join_event_ = nullptr;
-  const void* checked_row_map_ = nullptr;
+  cudaEvent_t raise_event_ = nullptr;
+  IndexCheckCache index_checks_;  // RA / RE tensors already validated
   bool nccl_transport_ = false;
   bool engine_ready_ = false;
   at::Tensor phase_trace_;

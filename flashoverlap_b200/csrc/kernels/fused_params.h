@@ -6,9 +6,10 @@
 // src/wait.cuh:5-9).  The GEMM phase writes every finished tile where its
 // consumer needs it (own memory or a peer's staging buffer) and bumps a counter
 // per 128-row block on the owning GPU; the reduce phase, run by the
-// same CTAs once they are out of tiles, waits (bounded) on those counters, sums
-// the per-rank partials in fp32, optionally applies RMSNorm and writes the
-// result locally (reduce-scatter) or to every peer (all-reduce).
+// communication warps of every CTA while the GEMM is still running (joined by
+// the GEMM warps once they are out of tiles), waits (bounded) on those
+// counters, sums the per-rank partials in fp32, optionally applies RMSNorm and
+// writes the result locally (reduce-scatter) or to every peer (all-reduce).
 #pragma once
 
 #include <cuda.h>
@@ -17,6 +18,26 @@
 namespace fo {
 
 constexpr int kMaxRanks = 8;
+
+// CTA shape of the fused kernel: 8 GEMM warps (TMA, MMA, TMEM, signalling, 4 x
+// epilogue) and one group of communication warps that reduces rows while the
+// GEMM runs.  A row of the reduce phase is always handled by kGroupWarps warps.
+constexpr int kGemmWarps = 8;
+constexpr int kCommWarps = 4;
+constexpr int kGroupWarps = 4;
+constexpr int kFusedThreads = 32 * (kGemmWarps + kCommWarps);
+
+// Layout of one counter set (32-bit words): arrival counters of the 128-row
+// blocks, the all-reduce delivery counter, the per-source counters of a
+// gathered A operand, the row-job counter of the reduce phase.
+constexpr int kMaxTileRows = 2048;
+constexpr int kFlagDone = kMaxTileRows;
+constexpr int kFlagAReady = kMaxTileRows + 8;
+constexpr int kFlagJob = kMaxTileRows + 32;
+constexpr int kFlagWords = kMaxTileRows + 64;
+
+// Entries (uint64) per CTA of the optional phase trace.
+constexpr int kTraceWords = 8;
 
 // Where an element (row, col) of a logical row-major matrix lives in memory.
 // tiled == 0: natural layout, offset = row * ld + col.
@@ -51,8 +72,10 @@ enum StatusCode : uint32_t {
   ST_TIMEOUT_GATHER = 5,  // an all-gathered operand shard never arrived
 };
 
-// Written by the device on the first error only; lives in device memory and is
-// read back by FusedEngine::read_status.
+// Written by the device on the first error only.  The word itself lives in
+// device memory (the first error wins an atomic compare-and-swap there); the
+// winner also copies the record into a mirror in mapped host memory, which the
+// host reads without synchronising before every fused call.
 struct StatusWord {
   uint32_t code;
   uint32_t rank;
@@ -104,7 +127,7 @@ struct alignas(64) FusedParams {
 
   // ---- reduce phase ---------------------------------------------------------
   int reduce;                      // 0 = kernel ends after the GEMM
-  int reduce_group;                // warps that share one row in the reduce phase: 1, 2, 4 or 8
+  uint32_t* job_counter;           // next owned row to reduce (zero at launch); rows are claimed in order
   const void* stage;               // this GPU's staging: [ws][rows_per_owner][N]
   uint32_t flag_target;            // value every arrival counter must reach
   int norm;                        // apply RMSNorm after the sum
@@ -130,12 +153,16 @@ struct alignas(64) FusedParams {
   uint32_t* mc_done;
 
   // ---- phase trace ----------------------------------------------------------
-  // Optional: per CTA {kernel start, end of the GEMM phase, end of the reduce
-  // phase, tiles computed} as %globaltimer nanoseconds, 4 x uint64 per CTA.
+  // Optional, kTraceWords x uint64 per CTA, times as %globaltimer nanoseconds:
+  // [0] kernel start, [1] end of the GEMM phase, [2] last row reduced by this
+  // CTA, [3] tiles computed, [4] first row reduced by this CTA (0 = none),
+  // [5] rows reduced by this CTA, [6] all rows delivered (CTA 0 of an
+  // all-reduce only), [7] unused.
   unsigned long long* phase_trace;
 
   // ---- failure reporting ----------------------------------------------------
   StatusWord* status;
+  StatusWord* status_mirror;  // mapped host memory, may be null
   unsigned long long timeout_ns;
 };
 

@@ -1,27 +1,33 @@
 // Persistent, warp-specialised sm_100a kernel: C = A * B^T on tcgen05 tensor
 // cores with TMEM accumulators, operands staged by TMA, and the collective that
 // follows the GEMM (all-reduce or reduce-scatter, optionally RMSNorm) fused in
-// through peer-to-peer stores and system-scope counters.
+// through peer-to-peer stores or NVLink SHARP (multimem) and system-scope
+// counters.
 //
-// CTA layout (256 threads, one CTA per SM, grid <= number of SMs):
+// CTA layout (384 threads, one CTA per SM, grid <= number of SMs):
 //   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor loads; with a
 //                               gathered A operand it first waits for the source
 //                               ranks whose rows the tile needs)
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma / tcgen05.commit)
-//   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end);
-//                               in all-gather / all-to-all mode it then pushes this
-//                               rank's rows of A to the other ranks
+//   warp 2      TMEM allocator (allocates 2 x BN columns, frees them at the end)
 //   warp 3      signalling     (one lane publishes finished tiles at system scope
 //                               and bumps the owners' arrival counters)
 //   warps 4-7   epilogue       (tcgen05.ld -> convert -> smem transpose ->
 //                               coalesced 16-byte stores, local or to a peer)
+//   warps 8-11  communication  (reduce phase: from the first cycle on they claim
+//                               owned rows in completion order, wait (bounded)
+//                               for the row's partials from every rank, sum them
+//                               in fp32, apply RMSNorm and deliver the row;
+//                               all-gather / all-to-all mode: they push this
+//                               rank's rows of A to the other ranks)
 // With CTAS == 2 two such CTAs form a cluster: both stage operands and run an
 // epilogue for their own 128 rows, the MMA warp of rank 0 issues for the pair.
-// After its last tile the whole CTA joins the reduce phase: groups of 1, 2, 4 or
-// 8 warps take one owned row at a time.
+// After its last tile the eight GEMM warps of a CTA join the reduce phase as two
+// more row groups, so the tail of the collective runs on every warp.
 //
 // Replaces, as one launch, the reference's signalling GEMM + wait kernel +
-// segmented NCCL calls (reference: src/overlap_impl.cu:221-328).
+// segmented NCCL calls (reference: src/overlap_impl.cu:221-328): communication
+// of finished rows runs under the computation of later tiles inside one kernel.
 #pragma once
 
 #include "fused_params.h"
@@ -33,17 +39,21 @@ namespace fo {
 // CTAS == 2: a cluster of two CTAs computes a 256 x BN tile with
 //   tcgen05.mma.cta_group::2; each CTA stages its own 128 rows of A and one
 //   half of the B tile, so every SM fetches a third less per FLOP.
-template <int BN_, int CTAS_ = 1>
+template <int BN_, int CTAS_ = 1, int BK_ = 64>
 struct TileTraits {
   static constexpr int CTAS = CTAS_;
   static constexpr int BM = 128;           // rows per CTA
   static constexpr int TILE_M = BM * CTAS;  // rows per tile
   static constexpr int BN = BN_;
-  static constexpr int BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
+  static constexpr int BK = BK_;       // K depth of one pipeline stage
+  static constexpr int ATOM_K = 64;    // 64 x 2 bytes = one 128-byte swizzle row; one TMA box
+  static constexpr int ATOMS = BK / ATOM_K;
   static constexpr int UMMA_K = 16;
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_ATOM_BYTES = BM * ATOM_K * 2;
+  static constexpr int A_BYTES = A_ATOM_BYTES * ATOMS;
   static constexpr int B_ROWS = BN / CTAS;  // rows of B staged by each CTA
-  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int B_ATOM_BYTES = B_ROWS * ATOM_K * 2;
+  static constexpr int B_BYTES = B_ATOM_BYTES * ATOMS;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_WARPS = 4;
   static constexpr int EPI_SLAB_BYTES = 32 * 128;  // 32 rows x 64 columns of 16-bit values
@@ -56,10 +66,12 @@ struct TileTraits {
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; power of two >= 32
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
+  static_assert(BK == 64 || BK == 128, "BK must be 64 or 128");
   static_assert(STAGES >= 3, "pipeline too shallow");
 };
 
-constexpr int kThreads = 256;
+constexpr int kThreads = kFusedThreads;  // 8 GEMM warps + 4 communication warps
+constexpr int kGemmThreads = 32 * kGemmWarps;
 
 // ---------------------------------------------------------------------------
 // helpers
@@ -74,16 +86,29 @@ __device__ __forceinline__ long long layout_offset(const OutLayout& L, int row, 
   return view_row * w + (s % L.rldn) * L.bn + col % L.bn;
 }
 
-__device__ __forceinline__ void report_error(StatusWord* st, uint32_t code, uint32_t rank, uint32_t where,
-                                             uint32_t seen, uint32_t want) {
+__device__ __forceinline__ void report_error(StatusWord* st, StatusWord* mirror, uint32_t code, uint32_t rank,
+                                             uint32_t where, uint32_t seen, uint32_t want) {
   if (st == nullptr) return;
   if (atomicCAS(&st->code, 0u, code) == 0u) {
     st->rank = rank;
     st->where = where;
     st->seen = seen;
     st->want = want;
+    if (mirror != nullptr) {  // details first, the code last: a host that sees the code sees the rest
+      volatile StatusWord* m = mirror;
+      m->rank = rank;
+      m->where = where;
+      m->seen = seen;
+      m->want = want;
+      __threadfence_system();
+      m->code = code;
+    }
     __threadfence_system();
   }
+}
+__device__ __forceinline__ void report_error(const FusedParams& p, uint32_t code, uint32_t where, uint32_t seen,
+                                             uint32_t want) {
+  report_error(p.status, p.status_mirror, code, static_cast<uint32_t>(p.me), where, seen, want);
 }
 
 template <bool BF16>
@@ -138,82 +163,62 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
 }
 
 // ---------------------------------------------------------------------------
-// reduce phase: a group of G warps per owned row (G = p.reduce_group)
+// reduce phase: groups of kGroupWarps warps, one owned row at a time
 // ---------------------------------------------------------------------------
-// Each group takes one row at a time: its warps wait (bounded) until the
-// partial rows of every rank have arrived, sum them in fp32 and round the sum
-// to the 16-bit type (the value an all-reduce would have produced).  Without
-// RMSNorm the rounded sum goes straight to its destination(s); with RMSNorm it
-// is parked in shared memory while the sum of squares is accumulated (combined
-// across the group's warps through a named barrier when G > 1), then scaled,
-// multiplied by the weight and written out.  Groups never synchronise with one
-// another, so every SM keeps several independent chains of loads in flight.
-// NVLS == true replaces the per-rank loads by one multimem.ld_reduce per chunk
-// and the per-rank result stores by one multimem.st.  WS > 0 fixes the number of ranks at compile time (all
-// loads of a batch are issued before the first use); WS == 0 is the generic
-// fallback for other group sizes.
-template <bool BF16, int WS, bool NVLS>
-__device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem, int smem_bytes, float* red,
-                                             int warp, int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
-  constexpr int BM = 128;
-  // NVLS: one load-reduce per chunk replaces the ws loads (instantiated with WS == 1)
-  constexpr int U = WS == 0 ? 1 : (WS == 1 ? 8 : (WS == 2 ? 4 : 2));  // chunks per lane per batch
-  constexpr int NS = WS == 0 ? kMaxRanks : WS;
-  constexpr int kWarps = kThreads / 32;
-  const int ws = NVLS ? p.ws : (WS == 0 ? p.ws : WS);
-  const int nsrc = NVLS ? 1 : ws;  // loads per chunk
-  const int n_chunks = p.N >> 3;  // 16-byte chunks per row
-  const int row_bytes = p.N * 2;
-  const uint32_t smem_base = ptx::smem_u32(smem);
-  // G warps share one row (G = 1, 2, 4 or 8); few rows per CTA -> larger G
-  const int G = p.reduce_group;
-  int groups = kWarps / G;
-  const int gidx = warp / G;  // row group of this warp
-  const int wg = warp - gidx * G;
+// Shared-memory scratch of one row group.
+struct GroupScratch {
+  uint32_t job[2];   // row claimed for iteration i lives in job[i & 1]
+  float ssq[kGroupWarps];
+  uint32_t pad[2];
+};
 
-  // RMSNorm: the weight vector is staged in shared memory once per CTA, then
-  // one row buffer per row group follows it.
-  if (p.norm) {
-    const uint16_t* gamma = reinterpret_cast<const uint16_t*>(p.gamma);
-    for (int c = threadIdx.x; c < n_chunks; c += kThreads) {
-      ptx::st_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4), *reinterpret_cast<const uint4*>(gamma + c * 8));
-    }
-    const int fit = (smem_bytes - row_bytes) / row_bytes;
-    if (fit < groups) groups = fit;
-    __syncthreads();
-  }
-  if (groups < 1 || gidx >= groups) return;  // (< 1 is rejected on the host)
-  const uint32_t gbuf = smem_base;
-  const uint32_t rowbuf = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(gidx + 1);
+__device__ __forceinline__ void group_barrier(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(kGroupWarps * 32) : "memory");
+}
+
+// Rows this rank owns are numbered lr = 0 .. rows_per_owner-1 in the order in
+// which the GEMM phase completes their tile rows (ascending: the raster walks
+// tile rows upwards from p.rot, and a rank's block is the last one it computes).
+// Every group claims the next row from a counter in global memory, so rows are
+// always taken in completion order by whichever warps are free: the
+// communication warps from the start, the GEMM warps once their tiles are done.
+// For one row the group waits (bounded) until the partials of every rank have
+// arrived, sums them in fp32 and rounds the sum to the 16-bit type (the value an
+// all-reduce would have produced).  Rows of up to 8192 values stay in registers
+// (8 x 16 bytes per thread) between the sum and the RMSNorm scaling; wider rows
+// take two passes (the rounded sums are parked in this rank's output row and read
+// back).  NVLS == true replaces the per-rank loads by one multimem.ld_reduce per
+// chunk and the per-rank result stores by one multimem.st.  WS > 0 fixes the
+// number of ranks at compile time; WS == 0 is the generic fallback.
+template <bool BF16, int WS, bool NVLS>
+__device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* gs, int group, int wg, int lane,
+                                            uint64_t deadline, volatile uint32_t* abort_flag) {
+  constexpr int BM = 128;
+  constexpr int GT = kGroupWarps * 32;  // threads per row
+  constexpr int CPT = 8;                // 16-byte chunks per thread held in registers
+  constexpr int NS = NVLS ? 1 : (WS == 0 ? kMaxRanks : WS);
+  constexpr int BATCH = NS >= CPT ? 1 : CPT / NS;  // chunks loaded together
+  const int ws = p.ws;
+  const int nsrc = NVLS ? 1 : ws;
+  const int n_chunks = p.N >> 3;
+  const bool one_pass = n_chunks <= GT * CPT;
+  const int tid = wg * 32 + lane;
   const int rows_local = p.rows_per_owner;
   const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
   const long long src_stride = static_cast<long long>(rows_local) * p.N;
   const uint32_t* my_flag = p.flag[p.me];
-  const int cl = wg * 32 + lane;  // first chunk of this lane
-  const int cstep = 32 * G;       // chunk stride between a lane's chunks
+  const uint4* gamma = reinterpret_cast<const uint4*>(p.gamma);
+  const bool leader = wg == 0 && lane == 0;
+  unsigned long long t_first = 0, t_last = 0;
+  uint32_t rows_done = 0;
 
-  auto load_batch = [&](uint4 (&v)[U][NS], const uint16_t* src0, int c0) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int c = c0 + cstep * u;
-      if (c < n_chunks) {
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-          if (s < nsrc) {
-            if constexpr (NVLS) v[u][s] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
-            else v[u][s] = ptx::ld_cg_v4(src0 + s * src_stride + c * 8);
-          }
-        }
-      }
-    }
-  };
   auto store_out = [&](int out_row, int c, const uint4& o) {
     const long long off = layout_offset(p.out_layout, out_row, c * 8);
     if (NVLS && p.bcast) {
       ptx::multimem_st_v4(reinterpret_cast<uint16_t*>(p.mc_out) + off, o);  // lands on every rank
     } else if (p.bcast) {
 #pragma unroll
-      for (int r = 0; r < NS; ++r) {
+      for (int r = 0; r < kMaxRanks; ++r) {
         if (r < ws) {
           int d = p.me + 1 + r;  // start with the next rank: owners spread over destinations
           if (d >= ws) d -= ws;
@@ -224,111 +229,180 @@ __device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem
       ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[p.me]) + off, o);
     }
   };
+  auto sum_sources = [&](const uint4 (&v)[NS]) -> uint4 {
+    if constexpr (NVLS) {
+      return v[0];  // summed by the switch in fp32, rounded once
+    } else {
+      float a[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = 0.f;
+#pragma unroll
+      for (int sidx = 0; sidx < NS; ++sidx) {
+        if (sidx < nsrc) {
+          float2 f;
+          f = unpack2<BF16>(v[sidx].x); a[0] += f.x; a[1] += f.y;
+          f = unpack2<BF16>(v[sidx].y); a[2] += f.x; a[3] += f.y;
+          f = unpack2<BF16>(v[sidx].z); a[4] += f.x; a[5] += f.y;
+          f = unpack2<BF16>(v[sidx].w); a[6] += f.x; a[7] += f.y;
+        }
+      }
+      uint4 h;
+      h.x = pack2<BF16>(a[0], a[1]);
+      h.y = pack2<BF16>(a[2], a[3]);
+      h.z = pack2<BF16>(a[4], a[5]);
+      h.w = pack2<BF16>(a[6], a[7]);
+      return h;
+    }
+  };
+  auto sq = [&](const uint4& h) -> float {
+    float2 f;
+    float r;
+    f = unpack2<BF16>(h.x); r = f.x * f.x + f.y * f.y;
+    f = unpack2<BF16>(h.y); r += f.x * f.x + f.y * f.y;
+    f = unpack2<BF16>(h.z); r += f.x * f.x + f.y * f.y;
+    f = unpack2<BF16>(h.w); r += f.x * f.x + f.y * f.y;
+    return r;
+  };
+  auto scale = [&](const uint4& h, float rstd, const uint4& w) -> uint4 {
+    float2 f;
+    uint4 o;
+    f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
+    f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
+    f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
+    f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
+    return o;
+  };
+  // sum of squares over the whole row: warp shuffle, then the group's warps through shared memory
+  auto row_ssq = [&](float ssq) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    if (lane == 0) gs->ssq[wg] = ssq;
+    group_barrier(group);
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGroupWarps; ++w) t += gs->ssq[w];
+    return t;
+  };
 
-  for (int i = 0;; ++i) {
-    const int lr = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (gidx + groups * i);
+  uint32_t claimed = 0;
+  if (leader) claimed = atomicAdd(p.job_counter, 1u);
+  for (int it = 0;; ++it) {
+    if (leader) gs->job[it & 1] = claimed;
+    group_barrier(group);
+    const int lr = static_cast<int>(gs->job[it & 1]);
     if (lr >= rows_local) break;
+    if (leader) claimed = atomicAdd(p.job_counter, 1u);  // the next row; its latency hides behind this row
     int g;  // global row
     if (p.own_mode == OWN_BLOCK) g = p.me * rows_local + lr;
     else if (p.own_mode == OWN_INTERLEAVE) g = lr * ws + p.me;
     else g = lr;
     const int rb = g / BM;
 
-    // wait until every rank's partials for tile row rb have arrived
+    // wait until every rank's partials for the 128-row block rb have arrived
     uint32_t ok = 1;
     if (lane == 0) {
       uint32_t seen = 0;
       if (!ptx::wait_counter_geq(my_flag + rb, p.flag_target, deadline, &seen)) {
-        report_error(p.status, ST_TIMEOUT_FLAG, p.me, rb, seen, p.flag_target);
+        report_error(p, ST_TIMEOUT_FLAG, rb, seen, p.flag_target);
         *abort_flag = 1;
         ok = 0;
       }
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();  // lane 0's acquire is ordered before the other lanes' loads of the partials
 
     const int out_row = p.bcast ? g : lr;
     // NVLS: partials sit at their global row in every rank's staging buffer
     const uint16_t* src0 = NVLS ? reinterpret_cast<const uint16_t*>(p.mc_stage) + static_cast<long long>(g) * p.N
                                 : stage + static_cast<long long>(lr) * p.N;
-    float ssq = 0.f;
-    if (ok) {
-      // software pipeline: the loads of batch k+1 are in flight while batch k is summed
-      uint4 cur[U][NS], nxt[U][NS];
-      load_batch(cur, src0, cl);
-      for (int c0 = cl; c0 < n_chunks; c0 += cstep * U) {
-        if (c0 + cstep * U < n_chunks) load_batch(nxt, src0, c0 + cstep * U);
+    auto load_chunk = [&](uint4 (&v)[NS], int c) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int c = c0 + cstep * u;
-          if (c < n_chunks) {
-            float a[8];
+      for (int sidx = 0; sidx < NS; ++sidx) {
+        if (sidx < nsrc) {
+          if constexpr (NVLS) v[sidx] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
+          else v[sidx] = ptx::ld_cg_v4(src0 + sidx * src_stride + c * 8);
+        }
+      }
+    };
+
+    if (one_pass) {
+      uint4 h[CPT];
+      float ssq = 0.f;
+      if (ok) {
+        // software pipeline: the loads of batch k+1 are in flight while batch k is summed
+        uint4 cur[BATCH][NS], nxt[BATCH][NS];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a[e] = 0.f;
+        for (int u = 0; u < BATCH; ++u) {
+          const int c = u * GT + tid;
+          if (c < n_chunks) load_chunk(cur[u], c);
+        }
 #pragma unroll
-            for (int s = 0; s < NS; ++s) {
-              if (s < nsrc) {
-                float2 f;
-                f = unpack2<BF16>(cur[u][s].x); a[0] += f.x; a[1] += f.y;
-                f = unpack2<BF16>(cur[u][s].y); a[2] += f.x; a[3] += f.y;
-                f = unpack2<BF16>(cur[u][s].z); a[4] += f.x; a[5] += f.y;
-                f = unpack2<BF16>(cur[u][s].w); a[6] += f.x; a[7] += f.y;
-              }
+        for (int b0 = 0; b0 < CPT; b0 += BATCH) {
+          if (b0 + BATCH < CPT) {
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+              const int c = (b0 + BATCH + u) * GT + tid;
+              if (c < n_chunks) load_chunk(nxt[u], c);
             }
-            uint4 h;
-            h.x = pack2<BF16>(a[0], a[1]);
-            h.y = pack2<BF16>(a[2], a[3]);
-            h.z = pack2<BF16>(a[4], a[5]);
-            h.w = pack2<BF16>(a[6], a[7]);
-            if (p.norm) {
-              float2 f;
-              f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
-              f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
-              f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
-              f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
-              ptx::st_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4), h);
-            } else {
-              store_out(out_row, c, h);
+          }
+#pragma unroll
+          for (int u = 0; u < BATCH; ++u) {
+            const int c = (b0 + u) * GT + tid;
+            if (c < n_chunks) {
+              h[b0 + u] = sum_sources(cur[u]);
+              if (p.norm) ssq += sq(h[b0 + u]);
+              else store_out(out_row, c, h[b0 + u]);
+            }
+          }
+          if (b0 + BATCH < CPT) {
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+#pragma unroll
+              for (int sidx = 0; sidx < NS; ++sidx) cur[u][sidx] = nxt[u][sidx];
             }
           }
         }
+      }
+      if (p.norm) {
+        ssq = row_ssq(ssq);
+        if (ok) {
+          const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-          for (int s = 0; s < NS; ++s) cur[u][s] = nxt[u][s];
+          for (int u = 0; u < CPT; ++u) {
+            const int c = u * GT + tid;
+            if (c < n_chunks) store_out(out_row, c, scale(h[u], rstd, __ldg(gamma + c)));
+          }
         }
       }
-    }
-    if (p.norm) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-      if (G > 1) {
-        // combine the partial sums of the G warps of this row group; the slot
-        // alternates with the row so that a fast warp cannot overwrite a value
-        // a slow warp of the same group has yet to read
-        float* slot = red + (i & 1) * kWarps + gidx * G;
-        if (lane == 0) slot[wg] = ssq;
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + gidx), "r"(G * 32) : "memory");
-        ssq = 0.f;
-        for (int w = 0; w < G; ++w) ssq += slot[w];
-      }
+    } else {
+      // wide rows: first pass sums and parks the rounded sums in this rank's output row
+      float ssq = 0.f;
+      uint16_t* park = reinterpret_cast<uint16_t*>(p.out[p.me]);
       if (ok) {
-        const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
-        // each lane re-reads exactly the chunks it wrote, so no barrier is needed for the row buffer
-#pragma unroll 4
-        for (int c = cl; c < n_chunks; c += cstep) {
-          const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
-          const uint4 w = ptx::ld_shared_v4(gbuf + (static_cast<uint32_t>(c) << 4));
-          float2 f;
-          uint4 o;
-          f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
-          f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
-          f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
-          f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
-          store_out(out_row, c, o);
+        for (int c = tid; c < n_chunks; c += GT) {
+          uint4 v[NS];
+          load_chunk(v, c);
+          const uint4 h = sum_sources(v);
+          if (p.norm) {
+            ssq += sq(h);
+            ptx::st_v4(park + layout_offset(p.out_layout, out_row, c * 8), h);
+          } else {
+            store_out(out_row, c, h);
+          }
+        }
+      }
+      if (p.norm) {
+        ssq = row_ssq(ssq);
+        if (ok) {
+          const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
+          for (int c = tid; c < n_chunks; c += GT) {  // every thread re-reads exactly the chunks it wrote
+            const uint4 h = ptx::ld_cg_v4(park + layout_offset(p.out_layout, out_row, c * 8));
+            store_out(out_row, c, scale(h, rstd, __ldg(gamma + c)));
+          }
         }
       }
     }
-    if (!ok) continue;  // keep taking part in the group barriers of later rows; their waits fail at once
+    if (!ok) continue;  // keep taking part in the group barriers; later waits fail at once
     if (p.bcast) {
       __syncwarp();  // every lane's stores of this row part precede the releases below
       if constexpr (NVLS) {
@@ -337,124 +411,44 @@ __device__ __forceinline__ void reduce_phase(const FusedParams& p, uint8_t* smem
         if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
       }
     }
+    if (p.phase_trace != nullptr && leader) {
+      t_last = ptx::globaltimer_ns();
+      if (t_first == 0) t_first = t_last;
+      ++rows_done;
+    }
+  }
+  if (p.phase_trace != nullptr && leader && rows_done != 0) {
+    unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
+    atomicMax(tr + 2, t_last);
+    atomicMin(tr + 4, t_first);
+    atomicAdd(tr + 5, static_cast<unsigned long long>(rows_done));
   }
 }
 
-// ---------------------------------------------------------------------------
-// reduce phase on a single GPU with RMSNorm: rows streamed through shared memory
-// ---------------------------------------------------------------------------
-// With one rank there is nothing to sum: the phase is RMSNorm over the product
-// the epilogue stored.  Eight warps per SM cannot hide memory latency with
-// register loads, so each warp keeps two row buffers in shared memory and lets
-// the bulk-copy engine fetch row i+1 (cp.async.bulk, completion on an mbarrier)
-// while it normalises row i out of shared memory.  Returns false without doing
-// anything when shared memory cannot hold two rows per warp for at least one
-// warp (the caller then takes the generic path).
+// (not inlined: the kernel calls it from two places, the communication warps
+// and the GEMM warps that join later)
 template <bool BF16>
-__device__ __forceinline__ bool reduce_phase_single(const FusedParams& p, uint8_t* smem, int smem_bytes,
-                                                    uint64_t* rbar, int warp, int lane, uint64_t deadline,
-                                                    volatile uint32_t* abort_flag) {
-  constexpr int BM = 128;
-  constexpr int kWarps = kThreads / 32;
-  const int n_chunks = p.N >> 3;
-  const int row_bytes = p.N * 2;
-  int active = ((smem_bytes - row_bytes) / row_bytes) / 2;  // warps that get two row buffers after the weight vector
-  if (active > kWarps) active = kWarps;
-  if (active < 1) return false;
-  const uint32_t smem_base = ptx::smem_u32(smem);
-  const uint16_t* gamma = reinterpret_cast<const uint16_t*>(p.gamma);
-  for (int c = threadIdx.x; c < n_chunks; c += kThreads) {
-    ptx::st_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4), *reinterpret_cast<const uint4*>(gamma + c * 8));
+__device__ __noinline__ void comm_dispatch(const FusedParams& p, GroupScratch* gs, int group, int wg, int lane,
+                                              uint64_t deadline, volatile uint32_t* abort_flag) {
+  if (p.nvls) {
+    comm_worker<BF16, 1, true>(p, gs, group, wg, lane, deadline, abort_flag);
+    return;
   }
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2 * kWarps; ++i) ptx::mbar_init(&rbar[i], 1);
-    ptx::mbar_fence_init();
-    ptx::fence_proxy_async_smem();
+  switch (p.ws) {
+    case 1: comm_worker<BF16, 1, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
+    case 2: comm_worker<BF16, 2, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
+    case 4: comm_worker<BF16, 4, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
+    case 8: comm_worker<BF16, 8, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
+    default: comm_worker<BF16, 0, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
   }
-  __syncthreads();
-  if (warp >= active) return true;
-  const uint32_t buf0 = smem_base + static_cast<uint32_t>(row_bytes) * static_cast<uint32_t>(1 + 2 * warp);
-  uint64_t* bar = rbar + 2 * warp;
-  const int rows_local = p.rows_per_owner;
-  const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
-  const uint32_t* my_flag = p.flag[p.me];
-  auto row_of = [&](int i) { return static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * (warp + active * i); };
-
-  // lane 0: wait for the row's tile row, then start the copy of row i into buffer b
-  auto issue = [&](int i, int b) -> uint32_t {
-    const int lr = row_of(i);
-    if (lr >= rows_local) return 1u;
-    const int rb = lr / BM;
-    uint32_t seen = 0;
-    if (!ptx::wait_counter_geq(my_flag + rb, p.flag_target, deadline, &seen)) {
-      report_error(p.status, ST_TIMEOUT_FLAG, p.me, rb, seen, p.flag_target);
-      *abort_flag = 1;
-      return 0u;
-    }
-    ptx::fence_proxy_async_all();  // the epilogue's generic-proxy stores before the async-proxy read
-    ptx::mbar_arrive_expect_tx(&bar[b], static_cast<uint32_t>(row_bytes));
-    ptx::bulk_load_1d(buf0 + static_cast<uint32_t>(b * row_bytes), stage + static_cast<long long>(lr) * p.N,
-                      static_cast<uint32_t>(row_bytes), &bar[b]);
-    return 1u;
-  };
-
-  uint32_t ok = 1;
-  if (lane == 0) ok = issue(0, 0);
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  uint32_t phases = 0;  // bit b: parity to wait for on buffer b
-  for (int i = 0; ok; ++i) {
-    const int lr = row_of(i);
-    if (lr >= rows_local) break;
-    const int b = i & 1;
-    // all lanes finished reading buffer b^1 (row i-1) at the __syncwarp below
-    if (lane == 0) ok = issue(i + 1, b ^ 1);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ptx::mbar_wait(&bar[b], (phases >> b) & 1u, deadline)) {
-      if (lane == 0) {
-        report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x600u + warp, i, lr);
-        *abort_flag = 1;
-      }
-      break;
-    }
-    phases ^= 1u << b;
-    const uint32_t rowbuf = buf0 + static_cast<uint32_t>(b * row_bytes);
-    float ssq = 0.f;
-#pragma unroll 4
-    for (int c = lane; c < n_chunks; c += 32) {
-      const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
-      float2 f;
-      f = unpack2<BF16>(h.x); ssq += f.x * f.x + f.y * f.y;
-      f = unpack2<BF16>(h.y); ssq += f.x * f.x + f.y * f.y;
-      f = unpack2<BF16>(h.z); ssq += f.x * f.x + f.y * f.y;
-      f = unpack2<BF16>(h.w); ssq += f.x * f.x + f.y * f.y;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-    const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
-#pragma unroll 4
-    for (int c = lane; c < n_chunks; c += 32) {
-      const uint4 h = ptx::ld_shared_v4(rowbuf + (static_cast<uint32_t>(c) << 4));
-      const uint4 w = ptx::ld_shared_v4(smem_base + (static_cast<uint32_t>(c) << 4));
-      float2 f;
-      uint4 o;
-      f = unpack2<BF16>(h.x); o.x = norm_pack2<BF16>(f.x, f.y, rstd, w.x);
-      f = unpack2<BF16>(h.y); o.y = norm_pack2<BF16>(f.x, f.y, rstd, w.y);
-      f = unpack2<BF16>(h.z); o.z = norm_pack2<BF16>(f.x, f.y, rstd, w.z);
-      f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
-      ptx::st_v4(reinterpret_cast<uint16_t*>(p.out[0]) + layout_offset(p.out_layout, lr, c * 8), o);
-    }
-    __syncwarp();
-    if (p.bcast && lane == 0 && p.done[0] != nullptr) ptx::red_release_sys_add(p.done[0], 1u);
-  }
-  return true;
 }
 
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <int BN, bool BF16, int CTAS>
+template <int BN, int BK_, bool BF16, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __grid_constant__ FusedParams p) {
-  using T = TileTraits<BN, CTAS>;
+  using T = TileTraits<BN, CTAS, BK_>;
   constexpr int BM = T::BM, BK = T::BK, STAGES = T::STAGES, TILE_M = T::TILE_M;
   // rank inside the CTA pair; rank 0 (the leader) issues the MMAs of the pair
   const uint32_t cta_rank = CTAS == 2 ? ptx::cluster_ctarank() : 0u;
@@ -475,7 +469,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* epi_prog = tmem_slot + 4;  // [4] tiles finished by each epilogue warp
-  float* red = reinterpret_cast<float*>(bars + 40);  // [2][8] partial sums of the reduce phase
+  uint64_t* pair_bar = bars + 2 * STAGES + 8;  // teardown handshake between the CTAs of a pair
+  GroupScratch* group_scratch = reinterpret_cast<GroupScratch*>(bars + 40);  // [3] row groups of the reduce phase
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -491,8 +486,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       ptx::mbar_init(&tfull_bar[i], 1);
       ptx::mbar_init(&tempty_bar[i], T::EPI_WARPS * CTAS);  // the leader hears from both epilogues
     }
+    ptx::mbar_init(pair_bar, 1);
     *abort_flag = 0;
     for (int i = 0; i < 4; ++i) epi_prog[i] = 0;
+    if (p.phase_trace != nullptr) {
+      unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
+      tr[0] = t_start;
+      tr[1] = tr[2] = tr[3] = tr[5] = tr[6] = tr[7] = 0;
+      tr[4] = ~0ull;
+    }
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
   }
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
             if (r_end <= r_begin || r_end <= a_row || r_begin >= a_row + BM) continue;
             uint32_t seen = 0;
             if (!ptx::wait_counter_geq(p.a_ready + r, p.a_ready_target, deadline, &seen)) {
-              report_error(p.status, ST_TIMEOUT_GATHER, p.me, r, seen, p.a_ready_target);
+              report_error(p, ST_TIMEOUT_GATHER, r, seen, p.a_ready_target);
               *abort_flag = 1;
               ok = false;
             }
@@ -549,7 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, deadline)) {
-            report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x100u + stage, kb, t);
+            report_error(p, ST_TIMEOUT_PIPE, 0x100u + stage, kb, t);
             *abort_flag = 1;
             ok = false;
             break;
@@ -557,12 +559,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           if constexpr (CTAS == 2) {
             // both CTAs' bytes are counted on the leader's barrier
             if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * T::STAGE_BYTES);
-            ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES, &p.tmA, &full_bar[stage], kb * BK, a_row);
-            ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES, &p.tmB, &full_bar[stage], kb * BK, b_row);
+#pragma unroll
+            for (int h = 0; h < T::ATOMS; ++h) {  // one box of 64 K-values per swizzle atom
+              ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                                    kb * BK + h * T::ATOM_K, a_row);
+              ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                                    kb * BK + h * T::ATOM_K, b_row);
+            }
           } else {
             ptx::mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
-            ptx::tma_load_2d(smem_a + stage * T::A_BYTES, &p.tmA, &full_bar[stage], kb * BK, a_row);
-            ptx::tma_load_2d(smem_b + stage * T::B_BYTES, &p.tmB, &full_bar[stage], kb * BK, b_row);
+#pragma unroll
+            for (int h = 0; h < T::ATOMS; ++h) {
+              ptx::tma_load_2d(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                               kb * BK + h * T::ATOM_K, a_row);
+              ptx::tma_load_2d(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                               kb * BK + h * T::ATOM_K, b_row);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -578,7 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         for (int r = 0; r < p.ws; ++r) {
           uint32_t seen = 0;
           if (!ptx::wait_counter_geq(p.a_ready + r, p.a_ready_target, deadline, &seen)) {
-            report_error(p.status, ST_TIMEOUT_GATHER, p.me, 0x100u + r, seen, p.a_ready_target);
+            report_error(p, ST_TIMEOUT_GATHER, 0x100u + r, seen, p.a_ready_target);
             break;
           }
         }
@@ -601,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
         if (!ptx::mbar_wait(&tempty_bar[buf], (use & 1u) ^ 1u, deadline)) {
-          report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x200u + buf, it, t);
+          report_error(p, ST_TIMEOUT_PIPE, 0x200u + buf, it, t);
           *abort_flag = 1;
           ok = false;
           break;
@@ -610,19 +622,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase, deadline)) {
-            report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x300u + stage, kb, t);
+            report_error(p, ST_TIMEOUT_PIPE, 0x300u + stage, kb, t);
             *abort_flag = 1;
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint64_t da = ptx::make_smem_desc_k_sw128(ptx::smem_u32(smem_a + stage * T::A_BYTES));
-          const uint64_t db = ptx::make_smem_desc_k_sw128(ptx::smem_u32(smem_b + stage * T::B_BYTES));
 #pragma unroll
-          for (int k = 0; k < BK / T::UMMA_K; ++k) {
-            // advancing K by 16 elements = 32 bytes = 2 descriptor address units
-            if constexpr (CTAS == 2) ptx::umma_f16_ss_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else ptx::umma_f16_ss(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int h = 0; h < T::ATOMS; ++h) {
+            const uint64_t da =
+                ptx::make_smem_desc_k_sw128(ptx::smem_u32(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES));
+            const uint64_t db =
+                ptx::make_smem_desc_k_sw128(ptx::smem_u32(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES));
+#pragma unroll
+            for (int k = 0; k < T::ATOM_K / T::UMMA_K; ++k) {
+              // advancing K by 16 elements = 32 bytes = 2 descriptor address units
+              const uint32_t acc = (kb | h | k) != 0 ? 1u : 0u;
+              if constexpr (CTAS == 2) ptx::umma_f16_ss_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, acc);
+              else ptx::umma_f16_ss(d_tmem, da + 2u * k, db + 2u * k, idesc, acc);
+            }
           }
           // frees the stage (in both CTAs of a pair) once the MMAs have read it
           if constexpr (CTAS == 2) ptx::umma_commit_pair(&empty_bar[stage], 3);
@@ -638,41 +656,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         }
       }
     }
-  } else if (warp == 2) {
-    // ===================== all-gather push =====================
-    // This rank's shard of A goes to every rank's gathered A, destination by
-    // destination: first its own copy (the GEMM starts there), then rank me-1
-    // (which works on this shard right after its own), me-2, ...  Warp 2 of every CTA takes an
-    // interleaved share; when a destination's share is written the warp fences
-    // at system scope and bumps that rank's shard counter.
-    if (p.ag_push) {
-      const long long stride = static_cast<long long>(gridDim.x) * 32;
-      const long long first = static_cast<long long>(blockIdx.x) * 32 + lane;
-      for (int j = 0; j < p.ws; ++j) {
-        int d = p.me - j;
-        if (d < 0) d += p.ws;
-        const long long chunks = p.ag_bytes[d] >> 4;
-        const char* src = static_cast<const char*>(p.ag_src[d]);
-        char* dst = static_cast<char*>(p.ag_dst[d]);
-        long long c = first;
-        for (; c + 7 * stride < chunks; c += 8 * stride) {
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(src + ((c + u * stride) << 4));
-#pragma unroll
-          for (int u = 0; u < 8; ++u) ptx::st_v4(dst + ((c + u * stride) << 4), v[u]);
-        }
-        for (; c < chunks; c += stride) {
-          ptx::st_v4(dst + (c << 4), *reinterpret_cast<const uint4*>(src + (c << 4)));
-        }
-        __syncwarp();
-        if (lane == 0) {
-          ptx::fence_acq_rel_sys();
-          ptx::red_relaxed_sys_add(p.ag_flag[d], 1u);
-        }
-      }
-    }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < kGemmWarps) {
     // ===================== epilogue =====================
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const uint32_t slab = ptx::smem_u32(smem_epi + q * T::EPI_SLAB_BYTES);
@@ -687,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       const uint32_t use = static_cast<uint32_t>(it >> 1);
       if (!ptx::mbar_wait(&tfull_bar[buf], use & 1u, deadline)) {
         if (lane == 0) {
-          report_error(p.status, ST_TIMEOUT_PIPE, p.me, 0x400u + buf, it, t);
+          report_error(p, ST_TIMEOUT_PIPE, 0x400u + buf, it, t);
           *abort_flag = 1;
         }
         ok = false;
@@ -826,55 +810,90 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           if (cta_rank == 0 && p.ticket_counter != nullptr) {  // completion order, once per tile
             const int ticket = atomicAdd(p.ticket_counter, 1);
             if (slot >= 0 && slot < num_tiles) p.trace[slot] = ticket;
-            else report_error(p.status, ST_BAD_INDEX, p.me, 0x500u, slot, num_tiles);
+            else report_error(p, ST_BAD_INDEX, 0x500u, slot, num_tiles);
           }
         }
       }
     }
   }
 
-  // ===================== teardown of the GEMM phase =====================
+  if (warp >= kGemmWarps) {
+    // ===================== communication warps =====================
+    const int cw = warp - kGemmWarps;
+    if (p.ag_push) {
+      // All-gather / all-to-all push.  This rank's rows of A go to every
+      // rank's gathered A, destination by destination: first its own copy (the
+      // GEMM starts there), then rank me-1 (which works on this shard right
+      // after its own), me-2, ...  Every communication warp of every CTA takes
+      // an interleaved share; when a destination's share is written the warp
+      // fences at system scope and bumps that rank's shard counter.
+      const long long stride = static_cast<long long>(gridDim.x) * (kCommWarps * 32);
+      const long long first = static_cast<long long>(blockIdx.x) * (kCommWarps * 32) + cw * 32 + lane;
+      for (int j = 0; j < p.ws; ++j) {
+        int d = p.me - j;
+        if (d < 0) d += p.ws;
+        const long long chunks = p.ag_bytes[d] >> 4;
+        const char* src = static_cast<const char*>(p.ag_src[d]);
+        char* dst = static_cast<char*>(p.ag_dst[d]);
+        long long c = first;
+        for (; c + 7 * stride < chunks; c += 8 * stride) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(src + ((c + u * stride) << 4));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) ptx::st_v4(dst + ((c + u * stride) << 4), v[u]);
+        }
+        for (; c < chunks; c += stride) {
+          ptx::st_v4(dst + (c << 4), *reinterpret_cast<const uint4*>(src + (c << 4)));
+        }
+        __syncwarp();
+        if (lane == 0) {
+          ptx::fence_acq_rel_sys();
+          ptx::red_relaxed_sys_add(p.ag_flag[d], 1u);
+        }
+      }
+    } else if (p.reduce) {
+      static_assert(kCommWarps == kGroupWarps, "the communication warps form one row group");
+      comm_dispatch<BF16>(p, group_scratch, 0, cw, lane, deadline, abort_flag);
+    }
+    return;
+  }
+
+  // ===================== teardown of the GEMM phase (GEMM warps only) =====================
+  __syncwarp();
   ptx::tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (CTAS == 2) ptx::cluster_sync();  // the partner may still read this CTA's operands / signal its barriers
+  ptx::named_barrier_sync(8, kGemmThreads);
+  if constexpr (CTAS == 2) {
+    // The partner may still read this CTA's operands or signal its barriers:
+    // each CTA tells the other that its GEMM warps are done and waits (bounded)
+    // to hear the same.
+    if (threadIdx.x == 0) {
+      ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(pair_bar), cta_rank ^ 1u));
+      if (!ptx::mbar_wait_cluster(pair_bar, 0u, deadline)) {
+        report_error(p, ST_TIMEOUT_PIPE, 0x700u, 0, 0);
+        *abort_flag = 1;
+      }
+    }
+    ptx::named_barrier_sync(8, kGemmThreads);
+  }
   if (warp == 2) {
     ptx::tc_fence_after_sync();
     if constexpr (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, T::TMEM_COLS);
     else ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
   }
   if (p.phase_trace != nullptr && threadIdx.x == 0) {
-    unsigned long long* tr = p.phase_trace + 4ull * blockIdx.x;
-    tr[0] = t_start;
+    unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
     tr[1] = ptx::globaltimer_ns();
-    tr[2] = 0;
     int mine = 0;
     for (int t = first_tile; t < num_tiles; t += tile_stride) ++mine;
     tr[3] = static_cast<unsigned long long>(mine);
   }
   if (!p.reduce || *abort_flag) return;
 
-  // ===================== reduce phase =====================
-  ptx::fence_proxy_async_smem();  // the pipeline's shared memory is reused through the generic proxy
-  constexpr int kRowSmem = T::STAGES * T::STAGE_BYTES + T::EPI_BYTES;
-  // barriers of the single-GPU row pipeline: behind the partial-sum scratch
-  uint64_t* rbar = bars + 48;
-  if (p.nvls) {
-    reduce_phase<BF16, 1, true>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag);
-  } else if (p.ws == 1 && p.norm && p.reduce_group == 1 &&
-             reduce_phase_single<BF16>(p, smem, kRowSmem, rbar, warp, lane, deadline, abort_flag)) {
-    // done: rows streamed through shared memory
-  } else {
-    switch (p.ws) {
-      case 1: reduce_phase<BF16, 1, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
-      case 2: reduce_phase<BF16, 2, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
-      case 4: reduce_phase<BF16, 4, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
-      case 8: reduce_phase<BF16, 8, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
-      default: reduce_phase<BF16, 0, false>(p, smem, kRowSmem, red, warp, lane, deadline, abort_flag); break;
-    }
-  }
-
-  if (p.phase_trace != nullptr && lane == 0) {
-    atomicMax(p.phase_trace + 4ull * blockIdx.x + 2, static_cast<unsigned long long>(ptx::globaltimer_ns()));
+  // ===================== reduce phase, joined by the GEMM warps =====================
+  {
+    const int group = 1 + warp / kGroupWarps;  // warps 0-3 -> group 1, warps 4-7 -> group 2
+    comm_dispatch<BF16>(p, group_scratch + group, group, warp % kGroupWarps, lane, deadline, abort_flag);
   }
 
   // All-reduce: the kernel may only end once every owner has delivered its
@@ -882,8 +901,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   if (p.bcast && blockIdx.x == 0 && threadIdx.x == 0 && p.done[p.me] != nullptr) {
     uint32_t seen = 0;
     if (!ptx::wait_counter_geq(p.done[p.me], p.done_target, deadline, &seen)) {
-      report_error(p.status, ST_TIMEOUT_DONE, p.me, 0, seen, p.done_target);
+      report_error(p, ST_TIMEOUT_DONE, 0, seen, p.done_target);
     }
+    if (p.phase_trace != nullptr) p.phase_trace[6] = ptx::globaltimer_ns();
   }
 }
 

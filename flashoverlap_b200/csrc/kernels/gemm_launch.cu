@@ -10,9 +10,24 @@
 
 #include <mutex>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "gemm_fused_sm100.cuh"
 
 namespace fo {
+
+#include "generated/algo_table.inc"
+
+TileConfig algo_config(int algo) { return kAlgoTable[(algo < 0 || algo >= kNumAlgos) ? 0 : algo]; }
+
+bool cooperative_launch_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("FLASHOVERLAP_COOPERATIVE");
+    return !(e != nullptr && (std::strcmp(e, "0") == 0 || std::strcmp(e, "off") == 0));
+  }();
+  return on;
+}
 
 namespace {
 
@@ -46,49 +61,23 @@ bool make_tensor_map(CUtensorMap* map, const void* base, int rows, int cols, int
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, bool BF16, int CTAS>
-cudaError_t launch_instance(const FusedParams& p, int grid, cudaStream_t stream) {
-  using T = TileTraits<BN, CTAS>;
-  auto kern = gemm_fused_sm100_kernel<BN, BF16, CTAS>;
-  static bool attr_set[16] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 16 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
-  if (CTAS == 1) {
-    kern<<<grid, kThreads, T::SMEM_BYTES, stream>>>(p);
-    return cudaGetLastError();
-  }
-  // CTA pairs: a cluster of two CTAs per tile
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = T::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, p);
-}
-
 }  // namespace
 
 int device_sm_count() {
-  static int cached[16] = {};
+  static int cached[kMaxDevices] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 16 && cached[dev] > 0) return cached[dev];
+  const bool slot = dev >= 0 && dev < kMaxDevices;
+  if (slot && cached[dev] > 0) return cached[dev];
   int n = 0;
   cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  if (dev < 16) cached[dev] = n;
+  if (slot) cached[dev] = n;
   return n;
+}
+
+cudaError_t prepare_fused(int algo, DType dtype) {
+  if (algo < 0 || algo >= kNumAlgos) return cudaErrorInvalidValue;
+  return kPrepareTable[algo][dtype == DT_BF16 ? 1 : 0]();
 }
 
 cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t stream, const char** why) {
@@ -108,7 +97,7 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
     *why = "A and B must be 16-byte aligned";
     return cudaErrorInvalidValue;
   }
-  // every CTA stages 128 rows of A and (for a CTA pair) half of the B tile
+  // every CTA stages 128 rows of A and (for a CTA pair) half of the B tile, 64 K-values per box
   if (!make_tensor_map(&p.tmA, g.A, g.M, g.K, 128, g.dtype) ||
       !make_tensor_map(&p.tmB, g.B, g.N, g.K, tc.bn / tc.ctas, g.dtype)) {
     *why = "cuTensorMapEncodeTiled failed";
@@ -122,41 +111,17 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
   if (p.raster_group <= 0) p.raster_group = 1;
   if (p.raster_group > p.TM) p.raster_group = p.TM;
   if (p.rot < 0 || p.rot >= p.TM) p.rot = 0;
-  if (p.reduce && p.norm && static_cast<long long>(g.N) * 4 > TileTraits<256, 1>::STAGES * TileTraits<256, 1>::STAGE_BYTES + TileTraits<256, 1>::EPI_BYTES) {
-    *why = "fused RMSNorm keeps a row in shared memory: N is too large (limit about 53000)";
-    return cudaErrorInvalidValue;
-  }
   int grid = g.sm_count > 0 ? g.sm_count : device_sm_count();
   const int sms = device_sm_count();
   if (grid > sms) grid = sms;  // every CTA must be resident: CTAs wait on one another's output
-  if (p.reduce) {
-    if (p.reduce_group != 1 && p.reduce_group != 2 && p.reduce_group != 4 && p.reduce_group != 8) {
-      // Rows are latency-bound, so as many as possible should be in flight:
-      // take the widest row group that still covers all owned rows in one
-      // round (8 / G rows per CTA at a time).
-      int gsel = 8;
-      while (gsel > 1 && static_cast<long long>(grid) * (8 / gsel) < p.rows_per_owner) gsel >>= 1;
-      p.reduce_group = gsel;
-    }
-    if (p.bcast) p.done_target *= static_cast<uint32_t>(p.reduce_group);  // one delivery count per warp and row
+  if (p.reduce && p.job_counter == nullptr) {
+    *why = "the reduce phase needs a row-job counter";
+    return cudaErrorInvalidValue;
   }
   if (!p.reduce && !p.force_full_grid && grid > p.TM * p.TN * tc.ctas) grid = p.TM * p.TN * tc.ctas;
   if (tc.ctas == 2 && grid < 2) grid = 2;
-  const bool bf16 = g.dtype == DT_BF16;
-  if (tc.ctas == 2) {
-    if (tc.bn == 256) {
-      return bf16 ? launch_instance<256, true, 2>(p, grid, stream) : launch_instance<256, false, 2>(p, grid, stream);
-    }
-    return bf16 ? launch_instance<128, true, 2>(p, grid, stream) : launch_instance<128, false, 2>(p, grid, stream);
-  }
-  switch (tc.bn) {
-    case 256:
-      return bf16 ? launch_instance<256, true, 1>(p, grid, stream) : launch_instance<256, false, 1>(p, grid, stream);
-    case 128:
-      return bf16 ? launch_instance<128, true, 1>(p, grid, stream) : launch_instance<128, false, 1>(p, grid, stream);
-    default:
-      return bf16 ? launch_instance<64, true, 1>(p, grid, stream) : launch_instance<64, false, 1>(p, grid, stream);
-  }
+  if (tc.ctas == 2) grid &= ~1;
+  return kLaunchTable[g.algo][g.dtype == DT_BF16 ? 1 : 0](p, grid, stream);
 }
 
 }  // namespace fo

@@ -10,20 +10,17 @@ namespace fo {
 enum DType : int { DT_F16 = 0, DT_BF16 = 1 };
 
 // Tile configurations selectable through the reference's `Algo` index
-// (reference: src/tiling/gemm_tiling.cuh:3-10 lists its six; these are the
-// tcgen05 shapes used here).  BK is always 64.
+// (reference: src/tiling/gemm_tiling.cuh:3-10 lists its six).  The table, the
+// per-instance source files and configs/AlgoDict.pt are written by
+// tool/generate_instances.py, as in the reference (tool/generate_instances.py:5-63).
 // ctas == 2: the tile is computed by a pair of CTAs (tcgen05.mma.cta_group::2),
 // 128 rows each.
 struct TileConfig {
   int bm, bn, bk;
   int ctas;
 };
-constexpr int kNumAlgos = 5;
-inline TileConfig algo_config(int algo) {
-  static const TileConfig table[kNumAlgos] = {
-      {128, 256, 64, 1}, {128, 128, 64, 1}, {128, 64, 64, 1}, {256, 256, 64, 2}, {256, 128, 64, 2}};
-  return table[(algo < 0 || algo >= kNumAlgos) ? 0 : algo];
-}
+#include "generated/algo_count.inc"  // constexpr int kNumAlgos = ...;
+TileConfig algo_config(int algo);
 
 struct GemmOperands {
   const void* A;  // [M, K] row-major
@@ -39,7 +36,20 @@ struct GemmOperands {
 // cudaSuccess or an error; *why (if not null) receives a static message.
 cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t stream, const char** why);
 
+// One-time set-up of an instance on the current device (its shared-memory
+// limit), so that a later launch_fused enqueues work only.
+cudaError_t prepare_fused(int algo, DType dtype);
+
 // Number of SMs of the current device (cached per device).
 int device_sm_count();
+
+// Per-device caches (kernel attributes, SM counts) hold this many devices;
+// a device with a higher index is handled uncached.
+constexpr int kMaxDevices = 64;
+
+// Fused launches are cooperative by default (the driver guarantees that all
+// CTAs are resident together, or refuses).  FLASHOVERLAP_COOPERATIVE=0 in the
+// environment turns the attribute off.
+bool cooperative_launch_enabled();
 
 }  // namespace fo

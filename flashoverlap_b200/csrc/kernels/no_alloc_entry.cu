@@ -14,10 +14,12 @@
 
 namespace {
 
-constexpr int kMaxTileRows = 2048;                       // counters, one per 128 rows
-constexpr size_t kCounterBytes = 16 * 1024;              // >= kMaxTileRows * 4, keeps the product 256-byte aligned
+using fo::kFlagWords;
+using fo::kMaxDevices;
+using fo::kMaxTileRows;                                  // arrival counters, one per 128 rows
+constexpr size_t kCounterBytes = 16 * 1024;              // >= kFlagWords * 4, keeps the product 256-byte aligned
 constexpr size_t kProductBytes = static_cast<size_t>(FO_NOALLOC_MAX_ELEMS) * 2;
-constexpr int kMaxDevices = 64;
+static_assert(kCounterBytes >= static_cast<size_t>(kFlagWords) * 4, "counter area too small");
 
 // [counters | product].  In host code this name is only a handle for
 // cudaGetSymbolAddress; the device address is looked up once per device.
@@ -56,8 +58,9 @@ extern "C" int fo_gemm_rmsnorm_noalloc(const void* A, const void* B, const void*
                   static_cast<long long>(M) * N, static_cast<long long>(FO_NOALLOC_MAX_ELEMS), 128 * kMaxTileRows);
     return fail(3, err, err_len, msg);
   }
-  if ((reinterpret_cast<uintptr_t>(gamma) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) {
-    return fail(1, err, err_len, "fo_gemm_rmsnorm_noalloc: gamma and out must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u) ||
+      (reinterpret_cast<uintptr_t>(gamma) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) {
+    return fail(1, err, err_len, "fo_gemm_rmsnorm_noalloc: A, B, gamma and out must be 16-byte aligned");
   }
 
   int dev = 0;
@@ -66,15 +69,18 @@ extern "C" int fo_gemm_rmsnorm_noalloc(const void* A, const void* B, const void*
   if (dev < 0 || dev >= kMaxDevices) return fail(4, err, err_len, "fo_gemm_rmsnorm_noalloc: device index out of range");
 
   // Set-up, once per device, with that device current: the device address of
-  // the scratch array (the host-side symbol is not usable as a pointer).
+  // the scratch array (the host-side symbol is not usable as a pointer) and the
+  // shared-memory limit of the kernel for both dtypes.
   DeviceSlot& slot = g_slots[dev];
   std::call_once(slot.once, [&slot] {
     void* ptr = nullptr;
     slot.error = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
     if (slot.error == cudaSuccess) slot.scratch = ptr;
+    if (slot.error == cudaSuccess) slot.error = fo::prepare_fused(0, fo::DT_F16);
+    if (slot.error == cudaSuccess) slot.error = fo::prepare_fused(0, fo::DT_BF16);
   });
   if (slot.error != cudaSuccess || slot.scratch == nullptr) {
-    return fail(5, err, err_len, "fo_gemm_rmsnorm_noalloc: cudaGetSymbolAddress failed for the scratch array");
+    return fail(5, err, err_len, "fo_gemm_rmsnorm_noalloc: set-up failed (cudaGetSymbolAddress / shared-memory limit)");
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -82,8 +88,8 @@ extern "C" int fo_gemm_rmsnorm_noalloc(const void* A, const void* B, const void*
   uint32_t* counters = reinterpret_cast<uint32_t*>(base);
   void* product = base + kCounterBytes;
 
-  // The counters keep the previous call's values: clear the part this call uses.
-  e = cudaMemsetAsync(counters, 0, static_cast<size_t>(M / 128) * sizeof(uint32_t), s);
+  // The counters keep the previous call's values: clear them.
+  e = cudaMemsetAsync(counters, 0, static_cast<size_t>(kFlagWords) * sizeof(uint32_t), s);
   if (e != cudaSuccess) return fail(6, err, err_len, cudaGetErrorString(e));
 
   fo::GemmOperands g{};
@@ -104,6 +110,7 @@ extern "C" int fo_gemm_rmsnorm_noalloc(const void* A, const void* B, const void*
   p.epi_base[0] = product;
   p.epi_layout.ld = N;
   p.flag[0] = counters;
+  p.job_counter = counters + fo::kFlagJob;
   p.raster_group = 4;
   p.reduce = 1;
   p.stage = product;

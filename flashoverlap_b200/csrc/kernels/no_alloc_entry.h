@@ -24,12 +24,13 @@
  * values plus the counters: 32 MiB + 16 KiB of device memory on every GPU that
  * loads the library, held until the process exits.  M * N must not exceed
  * FO_NOALLOC_MAX_ELEMS, M must be a multiple of 128 (at most 128 * 2048), N a
- * multiple of 256, K a multiple of 8; anything else is refused with an error
- * message and nothing is launched.
+ * multiple of 256, K a multiple of 8, and all four pointers 16-byte aligned;
+ * anything else is refused with an error message before any work is enqueued.
+ * At most 64 devices per process (device index 0..63).
  *
  * First call.  The first call on each device looks up the device address of
  * the scratch array (cudaGetSymbolAddress) and raises the kernel's
- * shared-memory limit.  Make that first call with the device current and
+ * shared-memory limit for both dtypes.  Make that first call with the device current and
  * outside of any stream capture; later calls on that device only enqueue work
  * on `stream`.
  *

@@ -2,6 +2,7 @@
 
 #include <nvtx3/nvToolsExt.h>
 
+#include <cstring>
 #include <sstream>
 #include <stdexcept>
 
@@ -24,12 +25,13 @@ void check_launch(cudaError_t e, const char* why, const char* op) {
     throw std::runtime_error(cuda_error_string(e, msg.c_str()));
   }
 }
-constexpr size_t kFlagWords = FusedEngine::kMaxTileRows + 64;
 }  // namespace
 
 FusedEngine::~FusedEngine() {
   if (status_dev_ != nullptr) cudaFree(status_dev_);
+  if (status_host_ != nullptr) cudaFreeHost(status_host_);
   status_dev_ = nullptr;
+  status_host_ = status_mirror_ = nullptr;
 }
 
 void FusedEngine::init(int rank, int world, AllGatherFn all_gather) {
@@ -41,13 +43,33 @@ void FusedEngine::init(int rank, int world, AllGatherFn all_gather) {
   if (status_dev_ == nullptr) {
     check(cudaMalloc(reinterpret_cast<void**>(&status_dev_), sizeof(StatusWord)), "cudaMalloc(status)");
     check(cudaMemset(status_dev_, 0, sizeof(StatusWord)), "cudaMemset(status)");
+    // mirror in mapped host memory: read by check_previous() without a synchronisation
+    check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), sizeof(StatusWord), cudaHostAllocMapped),
+          "cudaHostAlloc(status mirror)");
+    std::memset(status_host_, 0, sizeof(StatusWord));
+    check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_mirror_), status_host_, 0),
+          "cudaHostGetDevicePointer(status mirror)");
   }
+}
+
+void FusedEngine::check_previous(const char* op) const {
+  if (status_host_ == nullptr) return;
+  const volatile StatusWord* m = status_host_;
+  if (m->code == ST_OK) return;
+  StatusWord s;
+  s.code = m->code;
+  s.rank = m->rank;
+  s.where = m->where;
+  s.seen = m->seen;
+  s.want = m->want;
+  throw std::runtime_error(std::string(op) + ": an earlier flashoverlap kernel reported a failure: " + describe(s) +
+                           "; its results are not valid (reset() clears the state)");
 }
 
 uint32_t* FusedEngine::flag_ptr(int rank, int set) const {
   return static_cast<uint32_t*>(heap_.ptr(rank, ws_.flags[set]));
 }
-uint32_t* FusedEngine::done_ptr(int rank, int set) const { return flag_ptr(rank, set) + kMaxTileRows; }
+uint32_t* FusedEngine::done_ptr(int rank, int set) const { return flag_ptr(rank, set) + kFlagDone; }
 
 namespace {
 size_t workspace_bytes(long long elems) {
@@ -67,6 +89,7 @@ void FusedEngine::carve_workspace(long long elems) {
   ws_.capacity_elems = elems;
   calls_ = 0;
   pushes_ = 0;
+  mm_arrivals_ = 0;
 }
 
 void FusedEngine::attach_symmetric(size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr) {
@@ -87,6 +110,16 @@ void FusedEngine::attach_symmetric(size_t bytes, const std::vector<void*>& peer_
   long long elems = static_cast<long long>((bytes - workspace_bytes(0)) / 8);
   if (elems < 1) throw std::runtime_error("attach_symmetric: buffer too small");
   carve_workspace(elems);
+}
+
+void FusedEngine::detach_symmetric() {
+  if (!heap_.valid() || heap_.owned()) return;
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  heap_.destroy();
+  ws_ = Workspace{};
+  calls_ = 0;
+  pushes_ = 0;
+  mm_arrivals_ = 0;
 }
 
 void FusedEngine::ensure_workspace(long long m, long long n) {
@@ -124,9 +157,9 @@ void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
   p.ws = world_;
   p.me = rank_;
   p.status = status_dev_;
+  p.status_mirror = status_mirror_;
   p.timeout_ns = timeout_ns_;
   p.raster_group = raster_group_;
-  p.reduce_group = reduce_group_;
   p.phase_trace = phase_trace_;
   p.epi_layout.ld = 0;
 }
@@ -135,6 +168,7 @@ void FusedEngine::gemm(const GemmOperands& g_in, void* C, const OutLayout* layou
                        cudaStream_t stream) {
   NvtxRange range("flashoverlap::gemm");
   if (!initialized()) init(0, 1, nullptr);
+  check_previous("gemm");
   FusedParams p;
   base_params(p, sig);
   GemmOperands g = g_in;
@@ -155,6 +189,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
                                cudaStream_t stream) {
   NvtxRange range("flashoverlap::gemm_rmsnorm");
   if (!initialized()) init(0, 1, nullptr);
+  check_previous("gemm_rmsnorm");
   ensure_workspace(1, 1);  // only the counters are needed
   GemmOperands g = g_in;
   if (g.sm_count == 0) g.sm_count = sm_count_;
@@ -174,6 +209,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   p.epi_base[0] = scratch;
   p.epi_layout.ld = g.N;
   p.flag[0] = local;
+  p.job_counter = local + kFlagJob;
   if (p.raster_group == 0) p.raster_group = 8;
   p.reduce = 1;
   p.stage = scratch;
@@ -192,6 +228,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
                                   const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream) {
   NvtxRange range("flashoverlap::gemm_allreduce");
   if (!initialized()) throw std::runtime_error("gemm_allreduce: engine not initialised");
+  check_previous("gemm_allreduce");
   GemmOperands g = g_in;
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
@@ -221,7 +258,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
     p.mc_stage = heap_.mc(ws_.stage[set]);
     p.mc_flag = static_cast<uint32_t*>(heap_.mc(ws_.flags[set]));
     p.mc_out = heap_.mc(ws_.result[set]);
-    p.mc_done = static_cast<uint32_t*>(heap_.mc(ws_.flags[set])) + kMaxTileRows;
+    p.mc_done = static_cast<uint32_t*>(heap_.mc(ws_.flags[set])) + kFlagDone;
   }
   // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
@@ -234,7 +271,8 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   p.bcast = 1;
   if (out_layout != nullptr) p.out_layout = *out_layout;
   else p.out_layout.ld = g.N;
-  p.done_target = static_cast<uint32_t>(g.M);
+  p.done_target = static_cast<uint32_t>(g.M) * kGroupWarps;  // one delivery count per warp and row
+  p.job_counter = flag_ptr(rank_, set) + kFlagJob;
   const char* why = nullptr;
   check_launch(launch_fused(g, p, stream, &why), why, "gemm_allreduce");
   ++calls_;
@@ -250,6 +288,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
                                      const OutLayout* out_layout, const SignalArgs* sig, cudaStream_t stream) {
   NvtxRange range("flashoverlap::gemm_reducescatter");
   if (!initialized()) throw std::runtime_error("gemm_reducescatter: engine not initialised");
+  check_previous("gemm_reducescatter");
   GemmOperands g = g_in;
   if (g.sm_count == 0) g.sm_count = sm_count_;
   const TileConfig tc = algo_config(g.algo);
@@ -293,6 +332,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   p.gamma = norm.gamma;
   p.eps = norm.eps;
   p.bcast = 0;
+  p.job_counter = flag_ptr(rank_, set) + kFlagJob;
   p.out[rank_] = D;
   if (out_layout != nullptr) p.out_layout = *out_layout;
   else p.out_layout.ld = g.N;
@@ -331,20 +371,20 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
   p.epi_layout.ld = N;
   if (p.raster_group == 0) p.raster_group = 2;
   p.rot = first_row / tc.bm;  // own rows first, then the blocks in the order they are pushed to this rank
-  p.a_ready = flag_ptr(rank_, set) + kMaxTileRows + 8;
+  p.a_ready = flag_ptr(rank_, set) + kFlagAReady;
   p.ag_push = 1;
   for (int r = 0; r < world_; ++r) {
     p.a_src_end[r] = src_end[r];
     p.ag_src[r] = src_for[r];
     p.ag_bytes[r] = bytes_for[r];
-    p.ag_flag[r] = flag_ptr(r, set) + kMaxTileRows + 8 + rank_;
+    p.ag_flag[r] = flag_ptr(r, set) + kFlagAReady + rank_;
   }
-  // every CTA pushes a share and bumps the counter once per destination
+  // every communication warp of every CTA pushes a share and bumps the counter once per destination
   int grid = sm_count_ > 0 ? sm_count_ : device_sm_count();
   if (grid > device_sm_count()) grid = device_sm_count();
   if (tc.ctas == 2) grid &= ~1;
   g.sm_count = grid;
-  p.a_ready_target = static_cast<uint32_t>(grid);
+  p.a_ready_target = static_cast<uint32_t>(grid) * kCommWarps;
   p.reduce = 0;
   p.force_full_grid = 1;
   // ag_dst is filled by the callers' layout: where my block lives on rank r
@@ -357,6 +397,7 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
 void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, int M, int N, int K, DType dtype,
                                  int algo, cudaStream_t stream) {
   if (!initialized()) throw std::runtime_error("allgather_gemm: engine not initialised");
+  check_previous("allgather_gemm");
   if (M % world_ != 0) throw std::runtime_error("allgather_gemm: M must be divisible by the world size");
   const int rows = M / world_;
   if (rows % 128 != 0) throw std::runtime_error("allgather_gemm: M / world must be a multiple of 128");
@@ -391,6 +432,7 @@ int FusedEngine::a2a_padded_rows(const int* mlen, int algo) const {
 void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int* mlen, int N, int K, DType dtype,
                            int algo, cudaStream_t stream) {
   if (!initialized()) throw std::runtime_error("a2a_gemm: engine not initialised");
+  check_previous("a2a_gemm");
   if (K % 8 != 0) throw std::runtime_error("a2a_gemm: K must be a multiple of 8");
   for (int i = 0; i < world_ * world_; ++i) {
     if (mlen[i] < 0) throw std::runtime_error("a2a_gemm: negative row count");
@@ -426,7 +468,20 @@ void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int
 
 void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {
   NvtxRange range("flashoverlap::p2p_push");
+  push_common(bytes, 0, ctas, stream);
+}
+
+void FusedEngine::p2p_push_bulk(long long bytes, int chunk_bytes, int ctas, cudaStream_t stream) {
+  NvtxRange range("flashoverlap::p2p_push_bulk");
+  if (chunk_bytes < 16 || chunk_bytes > 16384 || chunk_bytes % 16 != 0) {
+    throw std::runtime_error("p2p_push_bulk: chunk_bytes must be a multiple of 16 in [16, 16384]");
+  }
+  push_common(bytes, chunk_bytes, ctas, stream);
+}
+
+void FusedEngine::push_common(long long bytes, int chunk_bytes, int ctas, cudaStream_t stream) {
   if (!initialized()) throw std::runtime_error("p2p_push: engine not initialised");
+  check_previous("p2p_push");
   if (bytes <= 0 || bytes % 16 != 0) throw std::runtime_error("p2p_push: bytes must be a positive multiple of 16");
   ensure_workspace(static_cast<long long>(world_) * bytes / 2 + 8, 1);
   if (ctas <= 0) ctas = device_sm_count();
@@ -441,14 +496,43 @@ void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {
     p.dst[r] = static_cast<char*>(heap_.ptr(r, ws_.result[0])) + static_cast<size_t>(rank_) * bytes;
     p.flag[r] = static_cast<uint32_t*>(heap_.ptr(r, ws_.misc));
   }
-  check(launch_p2p_push(p, ctas, stream), "p2p_push launch");
+  if (chunk_bytes > 0) check(launch_p2p_push_bulk(p, chunk_bytes, ctas, stream), "p2p_push_bulk launch");
+  else check(launch_p2p_push(p, ctas, stream), "p2p_push launch");
   pushes_ += static_cast<unsigned long long>(world_ - 1) * ctas;  // arrivals expected here so far
   if (world_ > 1) {
     const uint32_t target = static_cast<uint32_t>(pushes_);
-    check(launch_wait_counter(static_cast<uint32_t*>(heap_.local(ws_.misc)), target, timeout_ns_, status_dev_, rank_,
+    check(launch_wait_counter(static_cast<uint32_t*>(heap_.local(ws_.misc)), target, timeout_ns_, status_dev_, status_mirror_, rank_,
                               stream),
           "wait_counter launch");
   }
+}
+
+void FusedEngine::multimem_bench(int kind, long long bytes, int ctas, DType dtype, cudaStream_t stream) {
+  NvtxRange range("flashoverlap::multimem_bench");
+  if (!initialized()) throw std::runtime_error("multimem_bench: engine not initialised");
+  check_previous("multimem_bench");
+  if (kind < MM_LD_REDUCE || kind > MM_ALLREDUCE) throw std::runtime_error("multimem_bench: unknown kind");
+  if (bytes <= 0 || bytes % (16 * world_) != 0) {
+    throw std::runtime_error("multimem_bench: bytes must be a positive multiple of 16 * world");
+  }
+  ensure_workspace(bytes / 2, 1);
+  if (!nvls_available()) throw std::runtime_error("multimem_bench: the symmetric memory has no multicast mapping");
+  if (ctas <= 0) ctas = device_sm_count();
+  MultimemParams p{};
+  p.kind = kind;
+  p.bf16 = dtype == DT_BF16;
+  p.mc_stage = heap_.mc(ws_.stage[0]);
+  p.mc_result = heap_.mc(ws_.result[0]);
+  p.local_src = heap_.local(ws_.stage[1]);
+  p.local_dst = heap_.local(ws_.result[1]);
+  p.bytes = bytes / world_;
+  p.offset = p.bytes * rank_;
+  p.mc_arrive = static_cast<uint32_t*>(heap_.mc(ws_.misc)) + 1;
+  check(launch_multimem(p, ctas, stream), "multimem launch");
+  mm_arrivals_ += static_cast<unsigned long long>(world_) * ctas;
+  check(launch_wait_counter(static_cast<uint32_t*>(heap_.local(ws_.misc)) + 1, static_cast<uint32_t>(mm_arrivals_),
+                            timeout_ns_, status_dev_, status_mirror_, rank_, stream),
+        "wait_counter launch");
 }
 
 void FusedEngine::wait_on_unset_counter(long long timeout_ms, cudaStream_t stream) {
@@ -457,7 +541,8 @@ void FusedEngine::wait_on_unset_counter(long long timeout_ms, cudaStream_t strea
   if (!heap_.valid()) throw std::runtime_error("wait_on_unset_counter: no workspace yet");
   // word 512 of the private counter page is never written by any kernel
   const uint32_t* never = static_cast<uint32_t*>(heap_.local(ws_.misc)) + 512;
-  check(launch_wait_counter(never, 1u, static_cast<unsigned long long>(timeout_ms) * 1000000ull, status_dev_, rank_,
+  check(launch_wait_counter(never, 1u, static_cast<unsigned long long>(timeout_ms) * 1000000ull, status_dev_,
+                            status_mirror_, rank_,
                             stream),
         "wait_counter launch");
 }
@@ -472,6 +557,7 @@ StatusWord FusedEngine::read_status() {
 
 void FusedEngine::clear_status() {
   if (status_dev_ != nullptr) check(cudaMemset(status_dev_, 0, sizeof(StatusWord)), "cudaMemset(status)");
+  if (status_host_ != nullptr) std::memset(status_host_, 0, sizeof(StatusWord));
 }
 
 void FusedEngine::reset_counters() {
@@ -493,6 +579,7 @@ void FusedEngine::reset_counters() {
   }
   calls_ = 0;
   pushes_ = 0;
+  mm_arrivals_ = 0;
   clear_status();
 }
 

@@ -44,7 +44,7 @@ struct SignalArgs {
 
 class FusedEngine {
  public:
-  static constexpr int kMaxTileRows = 2048;
+  static constexpr int kMaxTileRows = fo::kMaxTileRows;
 
   FusedEngine() = default;
   ~FusedEngine();
@@ -57,10 +57,8 @@ class FusedEngine {
   void set_timeout_ms(long long ms) { timeout_ns_ = static_cast<unsigned long long>(ms) * 1000000ull; }
   void set_sm_count(int n) { sm_count_ = n; }
   void set_raster_group(int g) { raster_group_ = g; }
-  // Warps sharing one row in the reduce phase (1, 2, 4, 8; 0 = choose from the row count).
-  void set_reduce_group(int g) { reduce_group_ = g; }
-  // Device buffer of 4 x uint64 per CTA that every following launch fills with
-  // its phase timestamps (null = off).
+  // Device buffer of kTraceWords x uint64 per CTA that every following launch
+  // fills with its phase timestamps (null = off).
   void set_phase_trace(unsigned long long* buf) { phase_trace_ = buf; }
 
   // C[M,N] = A[M,K] * B[N,K]^T on this GPU only.  `layout` null = row-major.
@@ -112,12 +110,21 @@ class FusedEngine {
   // other ranks with the push kernel and then waits, on the device, until the
   // pushes of all peers have landed here.  Used by the bandwidth-curve tool.
   void p2p_push(long long bytes, int ctas, cudaStream_t stream);
+  // Same transfer with bulk copies out of shared memory (`chunk_bytes` per copy).
+  void p2p_push_bulk(long long bytes, int chunk_bytes, int ctas, cudaStream_t stream);
+  // Collective NVLink SHARP primitive over `bytes` of symmetric memory (needs a
+  // multicast mapping): kind MM_LD_REDUCE / MM_ST / MM_ALLREDUCE, every rank
+  // handles its 1/world share, then waits until all ranks are done.
+  void multimem_bench(int kind, long long bytes, int ctas, DType dtype, cudaStream_t stream);
 
   // Collective.  Hands the engine externally allocated symmetric memory (see
   // SymmHeap::attach) to carve its workspace from; with a multicast mapping
   // the fused operations switch to the NVLink SHARP path.  The memory is
   // zero-filled here and must outlive the engine.
   void attach_symmetric(size_t bytes, const std::vector<void*>& peer_ptrs, void* mc_ptr);
+  // Collective.  Gives attached memory back (after draining the device): the
+  // next fused call allocates the engine's own peer-mapped heap.
+  void detach_symmetric();
   bool nvls_available() const { return heap_.valid() && heap_.has_multicast() && world_ > 1; }
   // Which operations take the NVLink SHARP path when it is available.
   // Default: all-reduce yes (it halves the inbound traffic), reduce-scatter no
@@ -135,6 +142,11 @@ class FusedEngine {
 
   // Collective.  Makes sure the symmetric workspace can hold an M x N problem.
   void ensure_workspace(long long m, long long n);
+
+  // Throws if a kernel launched earlier by this engine has reported a failure
+  // (reads the host mirror of the status word; no synchronisation).  Every
+  // operation calls it first, so a timed-out wait cannot pass unnoticed.
+  void check_previous(const char* op) const;
 
   // Reads the device status word (synchronises the device).  code == ST_OK
   // means no kernel has reported a failure since the last clear.
@@ -163,10 +175,11 @@ class FusedEngine {
   SymmHeap heap_;
   Workspace ws_;
   StatusWord* status_dev_ = nullptr;
+  StatusWord* status_host_ = nullptr;    // mirror of the status word in mapped host memory (host address)
+  StatusWord* status_mirror_ = nullptr;  // the same memory as the device sees it
   unsigned long long timeout_ns_ = 20000000000ull;
   int sm_count_ = 0;
   int raster_group_ = 0;  // 0 = choose per operation
-  int reduce_group_ = 0;
   bool use_nvls_ = true;
   bool use_nvls_rs_ = false;
   void carve_workspace(long long elems);
@@ -176,6 +189,8 @@ class FusedEngine {
   unsigned long long calls_ = 0;  // fused collective calls issued so far
   void* ag_dst_scratch_[kMaxRanks] = {};  // destination of this rank's block on every rank (per call)
   unsigned long long pushes_ = 0;  // arrivals expected at the push counter so far
+  unsigned long long mm_arrivals_ = 0;  // arrivals expected at the multimem benchmark counter so far
+  void push_common(long long bytes, int chunk_bytes, int ctas, cudaStream_t stream);
 };
 
 }  // namespace fo

@@ -105,26 +105,39 @@ def make_overlap_impl(group=None, timeout_ms: Optional[int] = None, nvls: Option
                       max_m: int = 8192, max_n: int = 8192):
     """An initialised ``OverlapImpl`` for the ranks of ``group`` (collective).
 
-    ``nvls`` (default: the ``FLASHOVERLAP_NVLS`` environment variable, else off)
-    asks for symmetric memory with an NVLink SHARP multicast mapping sized for
-    problems up to ``max_m x max_n``; the fused all-reduce then reduces with
-    ``multimem`` instructions.  Without it, or when the mapping cannot be made,
-    the object allocates peer-mapped memory itself on first use and its fused
-    operations move data with peer-to-peer stores (measured equally fast on
-    8 B200s, and independent of multicast support)."""
+    ``nvls`` (default: on, unless ``FLASHOVERLAP_NVLS=0``) asks for symmetric
+    memory with an NVLink SHARP multicast mapping sized for problems up to
+    ``max_m x max_n``; the fused all-reduce then reduces with ``multimem``
+    instructions (the switch adds the partial tiles and multicasts the
+    results, which moves about a third fewer bytes per NVLink direction than
+    two rounds of peer-to-peer stores).  The ranks agree on the outcome: if the
+    mapping cannot be made on ANY rank, every rank falls back together to the
+    peer-mapped memory the object allocates itself on first use, and the fused
+    operations move data with peer-to-peer stores."""
     rank, world = _world(group)
     impl = torch.classes.flashoverlap_class.OverlapImpl()
     impl.nccl_init(rank, world, broadcast_nccl_id(group))
     impl.cutlass_init()
     impl.overlap_init()
     if nvls is None:
-        nvls = os.environ.get("FLASHOVERLAP_NVLS", "0") in ("1", "true", "on")
-    if nvls and world > 1 and torch.cuda.is_available() and dist.get_backend(group) == "nccl":
+        nvls = os.environ.get("FLASHOVERLAP_NVLS", "1") not in ("0", "false", "off")
+    if (nvls and world > 1 and torch.cuda.is_available() and dist.get_backend(group) == "nccl"
+            and impl.transport() == "p2p"):
+        err = None
         try:
             attach_symmetric_memory(impl, workspace_bytes(max_m, max_n), group)
-        except Exception as exc:  # fall back to the object's own peer-mapped heap
+        except Exception as exc:  # noqa: BLE001  (any failure means "no multicast here")
+            err = exc
+        # every rank learns whether every rank succeeded; a partial success would leave some ranks on the
+        # attached memory and others in the collective set-up of their own heap
+        flag = torch.tensor([0 if err is None else 1], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()) != 0:
+            if err is None:
+                impl.detach_symmetric()
             if rank == 0:
-                print(f"flashoverlap_b200: symmetric memory with multicast unavailable ({exc!r}); using P2P stores")
+                why = repr(err) if err is not None else "another rank could not map it"
+                print(f"flashoverlap_b200: symmetric memory with multicast unavailable ({why}); using P2P stores")
     env = os.environ.get("FLASHOVERLAP_TIMEOUT_MS")
     if timeout_ms is None and env:
         timeout_ms = int(env)

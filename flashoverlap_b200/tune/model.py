@@ -136,11 +136,17 @@ def best_segmentation(M: int, N: int, gemm_ms: float, curve: torch.Tensor, tile_
     return best, best_ms
 
 
-def hint_from_samples(samples: torch.Tensor, wave_size: int) -> Tuple[bool, List[int]]:
+def hint_from_samples(samples: torch.Tensor, wave_size: int, min_agree: int = 0) -> Tuple[bool, List[int]]:
     """Tile order from completion-ticket samples ``[n_samples, tiles]``: every
     tile goes to the wave (ticket // wave_size) it lands in most often; waves are
     then trimmed to exactly ``wave_size`` tiles, keeping the tiles that agreed
-    most, and topped up from the surplus.  Returns (consistent, hint)."""
+    most, and topped up from the surplus.  Returns (consistent, hint).
+
+    ``min_agree`` > 0 is the stricter rule of the reference's multi-node search
+    (reference: tune/search_multinode.py:165-182): a tile only counts for its
+    wave when it landed there in at least ``min_agree`` samples (9 of 10
+    there); if that leaves a wave short by more than the surplus can fill, the
+    order is reported inconsistent."""
     samples = torch.as_tensor(samples).to(torch.long).cpu()
     if samples.dim() != 2 or samples.numel() == 0:
         raise ValueError("samples must be [n_samples, tiles]")
@@ -155,6 +161,10 @@ def hint_from_samples(samples: torch.Tensor, wave_size: int) -> Tuple[bool, List
     for w in range(waves):
         members = (modes == w).nonzero(as_tuple=True)[0].tolist()
         members.sort(key=lambda t: (-int(agree[t]), -t))
+        if min_agree > 0:
+            unsure = [t for t in members if int(agree[t]) < min_agree]
+            if len(unsure) * 10 > max(1, len(members)):  # more than a tenth of the wave is unstable
+                return False, []
         assigned.append(members[:targets[w]])
         surplus.extend(members[targets[w]:])
     for w in range(waves):
@@ -165,30 +175,38 @@ def hint_from_samples(samples: torch.Tensor, wave_size: int) -> Tuple[bool, List
     return ok, hint
 
 
-def predict_fused_ms(M: int, N: int, gemm_ms: float, world_size: int, comm_op: str, p2p_gbs: float,
-                     hbm_gbs: float = 6500.0, elem_bytes: int = 2, tail_us_per_row_round: float = 4.0,
-                     sm_count: int = 148, reduce_group: int = 1) -> float:
-    """Cost model of this library's fused kernel (one launch: GEMM phase that
-    pushes partial tiles to their owners, then a reduce phase).
+def predict_fused_ms(M: int, N: int, gemm_ms: float, world_size: int, comm_op: str, link_gbs: float,
+                     transport: str = "p2p", hbm_gbs: float = 6500.0, elem_bytes: int = 2, tile_m: int = 256,
+                     raster_group: int = 2, sm_count: int = 148, latency_us: float = 8.0) -> float:
+    """Cost model of this library's fused kernel: one launch in which the
+    communication warps reduce and deliver finished rows while the tensor cores
+    compute later tiles.
 
-    * GEMM phase: the slower of the GEMM itself and pushing (n-1)/n of the output
-      over NVLink at ``p2p_gbs`` (measured store bandwidth out of one GPU).
-    * reduce phase: every rank reads n partial copies of its M/n rows from HBM;
-      an all-reduce then stores those rows to all n ranks (again (n-1)/n of the
-      output over NVLink), a reduce-scatter stores them once locally.  Rows are
-      processed ``sm_count * 8 / reduce_group`` at a time with a fixed latency per
-      round.
+    * The GEMM and the collective overlap, so the body costs the slower of the
+      two: ``gemm_ms`` against the bytes one GPU must move per NVLink direction
+      at ``link_gbs`` (the MEASURED bandwidth of the transport, from the curve
+      files).  Bytes per direction, with S = M*N*elem_bytes and n ranks:
+      all-reduce over peer-to-peer stores 2*S*(n-1)/n (partials out, results
+      out), all-reduce over NVLink SHARP S*(1+1/n) (the switch pulls every
+      partial once and multicasts every result once), reduce-scatter S*(n-1)/n
+      (or S over NVLink SHARP).
+    * What cannot overlap is the tail: the rows of the last ``raster_group`` tile
+      rows can only be reduced once the GEMM has ended.  Their bytes go over the
+      link after the last tile, plus one round-trip latency.
+    * With one rank the "link" is HBM: the rows are read and written once.
     """
     n = max(world_size, 1)
-    out_bytes = float(M) * N * elem_bytes
-    link_ms = out_bytes * (n - 1) / n / (p2p_gbs * 1e9) * 1e3 if n > 1 else 0.0
-    phase1 = max(gemm_ms, link_ms)
-    rows = M // n
-    rounds = div_up(rows, max(1, sm_count * 8 // max(reduce_group, 1)))
-    read_ms = out_bytes / (hbm_gbs * 1e9) * 1e3  # n copies of 1/n of the matrix
-    if comm_op == "all_reduce":
-        phase2 = max(link_ms, read_ms) + out_bytes / n / (hbm_gbs * 1e9) * 1e3
+    S = float(M) * N * elem_bytes
+    if n == 1:
+        per_dir = 2.0 * S
+        bw = hbm_gbs
+    elif comm_op == "all_reduce":
+        per_dir = S * (1.0 + 1.0 / n) if transport == "nvls" else 2.0 * S * (n - 1) / n
+        bw = link_gbs
     else:
-        phase2 = read_ms + out_bytes / n / (hbm_gbs * 1e9) * 1e3
-    phase2 += rounds * tail_us_per_row_round * 1e-3
-    return phase1 + phase2
+        per_dir = S if transport == "nvls" else S * (n - 1) / n
+        bw = link_gbs
+    comm_ms = per_dir / (bw * 1e9) * 1e3
+    tail_rows = min(M, tile_m * max(raster_group, 1))
+    tail_ms = comm_ms * tail_rows / M + latency_us * 1e-3
+    return max(gemm_ms, comm_ms * (1.0 - tail_rows / M)) + tail_ms

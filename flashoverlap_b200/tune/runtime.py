@@ -30,8 +30,10 @@ def world() -> Tuple[int, int]:
     return 0, 1
 
 
-def mean_time_ms(fn: Callable[[], None], warmup: int = 20, reps: int = 200, flush: bool = False) -> float:
-    """Mean device time of ``fn`` in ms, maximum over the ranks."""
+def mean_time_ms(fn: Callable[[], None], warmup: int = 20, reps: int = 200, flush: bool = False,
+                 return_local: bool = False):
+    """Mean device time of ``fn`` in ms, maximum over the ranks (with
+    ``return_local`` also this rank's own mean)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -45,6 +47,8 @@ def mean_time_ms(fn: Callable[[], None], warmup: int = 20, reps: int = 200, flus
         ends[i].record()
     torch.cuda.synchronize()
     local = sum(s.elapsed_time(e) for s, e in zip(starts, ends)) / reps
+    if return_local:
+        return max_over_ranks(local), local
     return max_over_ranks(local)
 
 
@@ -78,7 +82,8 @@ def profile_gemm(impl, M: int, N: int, K: int, dtype=torch.float16, warmup: int 
 
 
 def compute_hint(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, wave_size: int, comm_op: str,
-                 dtype=torch.float16, warmup: int = 20, samples: int = 20) -> Tuple[bool, List[int]]:
+                 dtype=torch.float16, warmup: int = 20, samples: int = 20, min_agree: int = 0
+                 ) -> Tuple[bool, List[int]]:
     """Measured tile completion order -> tile-order hint (reference:
     tune/search.py:131-291).  Runs the fused operation in monitor mode with the
     identity order, collects the completion ticket of every tile ``samples``
@@ -119,7 +124,7 @@ def compute_hint(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, wave
             got[i] = MM[1:].reshape(-1)
         torch.cuda.synchronize()
         impl.check_status()
-        ok, hint = hint_from_samples(got.cpu(), wave_size)
+        ok, hint = hint_from_samples(got.cpu(), wave_size, min_agree)
     except RuntimeError as exc:
         dbg(f"compute_hint: sampling failed: {exc}")
     if ws > 1:
@@ -136,10 +141,14 @@ def compute_hint(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, wave
 
 def perf_running(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, cseg: Sequence[int],
                  hint: Sequence[int], comm_op: str, dtype=torch.float16, warmup: int = 20, reps: int = 200,
-                 raster_group: int = 0, reduce_group: int = 0) -> float:
+                 raster_group: int = 0, two_stream: bool = False, gemm_ctas: int = 0) -> float:
     """Mean time (ms, MAX over ranks) of the overlapped operation for one
-    solution; a single group means "no overlap": GEMM, then one collective
-    (reference: tune/search.py:357-459)."""
+    solution (reference: tune/search.py:357-459).  A single group means "no
+    overlap": GEMM, then one collective.  ``two_stream=False`` runs this
+    library's fused kernel through the reference-compatible entry point (the
+    wave grouping does not change what that kernel does); ``two_stream=True``
+    runs the reference's own design (signalling GEMM, stream waits, one NCCL
+    call per wave group on a second stream), whose speed the grouping decides."""
     _, ws = world()
     tm, tn = div_up(M, BM), div_up(N, BN)
     tiles = tm * tn
@@ -151,19 +160,86 @@ def perf_running(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, cseg
     D = torch.empty((M // ws, N), dtype=dtype, device="cuda") if comm_op == "reduce_scatter" else None
     RE = generate_row_mapping(M, N, BM, BN, list(cseg), ws, device="cuda") if comm_op == "reduce_scatter" else None
     impl.set_raster_group(raster_group)
-    impl.set_reduce_group(reduce_group)
     if len(cseg) == 1:
         if comm_op == "all_reduce":
             fn = lambda: impl.gemm_allreduce(A, B, C, algo)  # noqa: E731
         else:
             fn = lambda: impl.gemm_reducescatter(A, B, C, D, algo)  # noqa: E731
+    elif two_stream and comm_op == "all_reduce":
+        fn = lambda: impl.gemm_allreduce_twostream(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, gemm_ctas)  # noqa: E731
+    elif two_stream:
+        fn = lambda: impl.gemm_reducescatter_twostream(A, B, C, D, MM, RA, RE, 1, cseg_cpu, cseg_gpu, algo,  # noqa: E731
+                                                       gemm_ctas)
     elif comm_op == "all_reduce":
         fn = lambda: impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg_cpu, cseg_gpu, algo, False)  # noqa: E731
     else:
         fn = lambda: impl.gemm_reducescatter_overlap(A, B, C, D, MM, RA, RE, 1, cseg_cpu, cseg_gpu, algo,  # noqa: E731
                                                      False)
-    ms = mean_time_ms(fn, warmup, reps)
-    impl.check_status()
-    impl.set_raster_group(0)
-    impl.set_reduce_group(0)
+    try:
+        ms = mean_time_ms(fn, warmup, reps)
+        impl.check_status()
+    finally:
+        impl.set_raster_group(0)
     return ms
+
+
+def wave_units(tiles: int, wave: int, max_units: int = 10) -> Tuple[int, int]:
+    """(units, tiles per unit): the wave count folded to at most ``max_units``
+    units, as the reference normalises it (reference: tune/search.py:545-548,564)."""
+    waves = div_up(tiles, wave)
+    per_unit = div_up(waves, max_units)
+    return div_up(waves, per_unit), per_unit * wave
+
+
+def search_two_stream(impl, M: int, N: int, K: int, algo: int, comm_op: str, dtype=torch.float16,
+                      curve: Optional[torch.Tensor] = None, gemm_ms: Optional[float] = None, max_units: int = 10,
+                      top_k: int = 0, warmup: int = 5, reps: int = 20, gemm_ctas: int = 0,
+                      hint: Sequence[int] = ()) -> Tuple[List[int], float, List[Tuple[List[int], float]]]:
+    """Searches the wave grouping ``cSeg`` of the reference's two-stream overlap
+    design by TIMING candidates (reference: tune/search.py:473-526 exhaustive,
+    :529-596 predictive).  Collective.
+
+    Every composition of the (folded) wave count is a candidate, minus the
+    reference's "cold start" rule (more than five groups with a first group
+    above two units).  Without a bandwidth ``curve`` all candidates are timed;
+    with one (and the GEMM time ``gemm_ms``) they are ranked by the pipeline
+    model and only the ``top_k`` best (default 3) are timed.  Returns
+    ``(best cSeg, its time in ms, [(cSeg, ms) for every timed candidate])``."""
+    from .model import compositions, predict_segmented_ms, scale_groups
+
+    rank, ws = world()
+    BM, BN, _ = ALGO_TILES[algo]
+    tiles = div_up(M, BM) * div_up(N, BN)
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    ctas_per_tile = BM // 128
+    gemm_sms = gemm_ctas if gemm_ctas > 0 else sms - 16
+    wave = max(1, gemm_sms // ctas_per_tile)
+    units, unit_tiles = wave_units(tiles, wave, max_units)
+    cands: List[List[int]] = []
+    for parts in compositions(units):
+        if len(parts) > 5 and parts[0] > 2:
+            continue
+        try:
+            g = scale_groups(parts, unit_tiles, tiles)
+        except ValueError:
+            continue
+        if comm_op == "reduce_scatter" and any((x * BM) % ws for x in g):
+            continue
+        if g not in cands:
+            cands.append(g)
+    if [tiles] not in cands:
+        cands.append([tiles])
+    if curve is not None and gemm_ms is not None:
+        scored = sorted(cands, key=lambda g: predict_segmented_ms(M, N, gemm_ms, curve, g, tiles, comm_op, ws, sms,
+                                                                  sms - gemm_sms))
+        cands = scored[:top_k if top_k > 0 else 3]
+    elif top_k > 0:
+        cands = cands[:top_k]
+    timed: List[Tuple[List[int], float]] = []
+    for g in cands:
+        ms = perf_running(impl, M, N, K, BM, BN, algo, g, hint, comm_op, dtype, warmup=warmup, reps=reps,
+                          two_stream=True, gemm_ctas=gemm_ctas)
+        dbg(f"search_two_stream: cSeg {g} -> {ms:.4f} ms")
+        timed.append((g, ms))
+    best = min(timed, key=lambda t: t[1])
+    return best[0], best[1], timed

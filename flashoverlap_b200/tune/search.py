@@ -1,34 +1,45 @@
 """Wave-group search (reference: tune/search.py:473-618).
 
-The reference's tuned quantities are the GEMM tile configuration, the
-tile-order hint and the wave grouping ``cSeg`` of its segmented collectives.
-This library's fused kernel signals per tile row instead of per wave group, so
-what decides its speed is the tile configuration and two kernel knobs (raster
-group, warps per row of the reduce phase).  The search therefore
+The reference tunes three things: the GEMM tile configuration, the tile-order
+hint and the wave grouping ``cSeg`` of its segmented collectives, the last by
+timing every composition of the wave count (exhaustive) or by predicting with
+a pipeline model on a measured bandwidth curve and timing the pick
+(predictive).  Both drivers exist here and do the same, for two consumers:
 
-1. picks the tile-order hint from measured completion order (as the reference),
-2. derives ``cSeg`` with the reference's pipeline model on the measured
-   bandwidth curve (kept in the file for readers of that format), and
-3. chooses (Algo, raster_group, reduce_group) either by timing every candidate
-   (exhaustive) or by ranking candidates with the fused-kernel cost model and
-   timing only the best few (predictive).
+* the reference's own two-stream design (``gemm_*_twostream``) and the
+  reference-compatible file format: ``cSeg`` is searched by TIMING compositions
+  on that path, exactly the reference's procedure;
+* this library's fused kernel, which signals per tile row instead of per wave
+  group: what decides its speed is the tile configuration, the raster group
+  (how many tile rows are walked together, i.e. how early rows complete: the
+  fused kernel's "wave group") and the transport.  Candidates
+  ``(Algo, raster_group)`` are timed (exhaustive) or ranked by a cost model
+  on measured link bandwidth and then timed (predictive).
+
+Every number a model uses comes from a measured curve file; nothing about the
+machine is typed in here.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
 from ..utils import config as cfg
-from .model import best_segmentation, compositions, div_up, predict_fused_ms, scale_groups
-from .runtime import compute_hint, dbg, perf_running, world
+from .model import best_segmentation, div_up, predict_fused_ms
+from .runtime import compute_hint, dbg, perf_running, search_two_stream, world
 
 RASTER_CHOICES = (1, 2, 4, 8)
-REDUCE_CHOICES = (0, 1, 2, 4, 8)
 
 
 def sm_count() -> int:
     return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+# Sampling rule of the tile-order hint: (samples, minimum agreement).  The
+# single-node search votes over 20 samples; the multi-node search of the
+# reference takes 10 and wants a tile in the same wave in 9 of them.
+HINT_RULE = {"samples": 20, "min_agree": 0}
 
 
 def find_hint(impl, M, N, K, BM_list, BN_list, Algo_list, comm_op, dtype, wave_units: int = 1, tries: int = 5):
@@ -38,89 +49,114 @@ def find_hint(impl, M, N, K, BM_list, BN_list, Algo_list, comm_op, dtype, wave_u
         BM, BN, algo = BM_list[t], BN_list[t], Algo_list[t]
         ctas = BM // 128
         wave = max(1, sms // ctas) * wave_units
-        ok, hint = compute_hint(impl, M, N, K, BM, BN, algo, wave, comm_op, dtype)
+        ok, hint = compute_hint(impl, M, N, K, BM, BN, algo, wave, comm_op, dtype, samples=HINT_RULE["samples"],
+                                min_agree=HINT_RULE["min_agree"])
         dbg(f"find_hint: candidate {t} ({BM}x{BN}, Algo {algo}) consistent={ok}")
         if ok:
             return t, hint
     raise RuntimeError("tuning failed: no tile configuration gave a consistent completion order")
 
 
-def knob_candidates(M: int, world_size: int) -> List[Tuple[int, int]]:
-    rows = M // max(world_size, 1)
-    out = []
-    for rg in RASTER_CHOICES:
-        for g in REDUCE_CHOICES:
-            if g and 148 * (8 // g) * 4 < rows and g > 1:
-                continue  # far too few rows in flight
-            out.append((rg, g))
-    return out
+def knob_candidates(M: int, BM: int) -> List[int]:
+    """Raster groups worth trying for a matrix of M rows and tiles of BM rows."""
+    tm = max(1, M // BM)
+    out = [rg for rg in RASTER_CHOICES if rg <= tm]
+    return out or [1]
+
+
+def _fused_time(impl, M, N, K, BM, BN, algo, comm_op, dtype, rg, reps):
+    tiles = div_up(M, BM) * div_up(N, BN)
+    return perf_running(impl, M, N, K, BM, BN, algo, [tiles - 1, 1] if tiles > 1 else [1], [], comm_op, dtype,
+                        warmup=10, reps=reps, raster_group=rg)
 
 
 def exhaustive_search(impl, M: int, N: int, K: int, comm_op: str, dtype=torch.float16, path=None,
-                      reps: int = 50, verbose: bool = True) -> dict:
-    """Times every (tile configuration, raster group, reduce group) candidate."""
+                      reps: int = 50, verbose: bool = True, max_units: int = 10, seg_reps: int = 20) -> dict:
+    """Times every fused candidate (tile configuration x raster group) and every
+    composition of the wave count on the two-stream path."""
     rank, ws = world()
     data = cfg.load_config(M, N, K, path)
     BM_l, BN_l, dur_l, Algo_l = cfg.stage1_lists(data)
     best = None
-    hints = {}
     for t in range(min(5, len(BM_l))):
         BM, BN, algo = BM_l[t], BN_l[t], Algo_l[t]
-        tiles = div_up(M, BM) * div_up(N, BN)
-        for rg, g in knob_candidates(M, ws):
-            ms = perf_running(impl, M, N, K, BM, BN, algo, [tiles - 1, 1] if tiles > 1 else [1], [], comm_op, dtype,
-                              warmup=10, reps=reps, raster_group=rg, reduce_group=g)
+        for rg in knob_candidates(M, BM):
+            ms = _fused_time(impl, M, N, K, BM, BN, algo, comm_op, dtype, rg, reps)
             if rank == 0 and verbose:
-                print(f"Algo {algo} ({BM}x{BN}) raster {rg} reduce {g}: {ms:.4f} ms")
+                print(f"Algo {algo} ({BM}x{BN}) raster {rg}: {ms:.4f} ms")
             if best is None or ms < best[0]:
-                best = (ms, t, rg, g)
-    ms, t, rg, g = best
+                best = (ms, t, rg)
+    ms, t, rg = best
     _, hint = find_hint(impl, M, N, K, BM_l[t:t + 1], BN_l[t:t + 1], Algo_l[t:t + 1], comm_op, dtype)
-    tiles = div_up(M, BM_l[t]) * div_up(N, BN_l[t])
-    wave = max(1, sm_count() // (BM_l[t] // 128))
-    cseg = scale_groups([1] * div_up(tiles, wave), wave, tiles)
+    # the reference's composition loop: every candidate grouping is timed
+    cseg, seg_ms, timed = search_two_stream(impl, M, N, K, Algo_l[t], comm_op, dtype, max_units=max_units,
+                                            reps=seg_reps, hint=hint)
+    if rank == 0 and verbose:
+        for g, tms in timed:
+            print(f"cSeg {g}: two-stream {tms:.4f} ms")
     sol = dict(BM=BM_l[t], BN=BN_l[t], dur=dur_l[t], Algo=Algo_l[t], hint=hint, cSeg=cseg, raster_group=rg,
-               reduce_group=g, fused_dur=ms, comm_op=comm_op, world_size=ws, search="exhaustive")
+               fused_dur=ms, two_stream_dur=seg_ms, candidates_timed=len(timed), comm_op=comm_op, world_size=ws,
+               search="exhaustive")
     if rank == 0:
         cfg.save_stage2(M, N, K, path=path, **sol)
         if verbose:
-            print(f"Best solution: Algo {sol['Algo']} raster {rg} reduce {g}, {ms:.4f} ms; solution saved.")
+            print(f"Best solution: Algo {sol['Algo']} raster {rg}, fused {ms:.4f} ms; cSeg {cseg}, two-stream "
+                  f"{seg_ms:.4f} ms; solution saved.")
     return sol
 
 
+def link_bandwidth_from_curves(world_size: int, multinode: bool = False, path=None) -> Tuple[Optional[float], str]:
+    """Peak of the measured curve of the transport the fused kernel uses
+    (NVLink SHARP all-reduce primitive if it was measured, else peer-to-peer
+    stores), in GB/s, and the name of the file it came from."""
+    for op in ("multimem_allreduce", "p2p_push_bulk", "p2p_push"):
+        try:
+            c = cfg.load_bandwidth(op, world_size, multinode, path)
+        except FileNotFoundError:
+            continue
+        return float(c[:, 1].max()), op
+    return None, ""
+
+
 def predictive_search(impl, M: int, N: int, K: int, comm_op: str, curve: torch.Tensor,
-                      p2p_gbs: Optional[float] = None, dtype=torch.float16, path=None, top_k: int = 3,
-                      reps: int = 50, verbose: bool = True) -> dict:
-    """Ranks candidates with the cost models, times only the ``top_k`` best."""
+                      link_gbs: Optional[float] = None, dtype=torch.float16, path=None, top_k: int = 3,
+                      reps: int = 50, verbose: bool = True, link_kind: str = "p2p", seg_reps: int = 20) -> dict:
+    """Ranks candidates with the cost models on measured bandwidth, then times
+    only the best few.  ``curve`` is the measured NCCL curve of ``comm_op``
+    (for the two-stream grouping), ``link_gbs`` the measured bandwidth of the
+    fused kernel's transport (``link_kind``: "p2p" or "nvls")."""
     rank, ws = world()
+    if link_gbs is None:
+        if ws > 1:
+            raise ValueError("predictive_search needs the measured link bandwidth (run tune/bandwidth.py --comm_op "
+                             "p2p_push or multimem_allreduce first)")
+        link_gbs = 1.0  # unused with one rank
     data = cfg.load_config(M, N, K, path)
     BM_l, BN_l, dur_l, Algo_l = cfg.stage1_lists(data)
-    if p2p_gbs is None:
-        p2p_gbs = 550.0  # store bandwidth out of one B200 through NVSwitch, measured with p2p_push
     ranked = []
     for t in range(min(10, len(BM_l))):
-        for rg, g in knob_candidates(M, ws):
-            geff = g or max(1, min(8, 8 // max(1, div_up(M // max(ws, 1), 148))))
-            est = predict_fused_ms(M, N, dur_l[t], ws, comm_op, p2p_gbs, reduce_group=geff)
-            est *= 1.0 + 0.01 * abs(rg - 2)  # mild preference for the default raster
-            ranked.append((est, t, rg, g))
+        for rg in knob_candidates(M, BM_l[t]):
+            est = predict_fused_ms(M, N, dur_l[t], ws, comm_op, link_gbs, transport=link_kind, tile_m=BM_l[t],
+                                   raster_group=rg)
+            ranked.append((est, t, rg))
     ranked.sort()
     best = None
-    for est, t, rg, g in ranked[:top_k]:
-        tiles = div_up(M, BM_l[t]) * div_up(N, BN_l[t])
-        ms = perf_running(impl, M, N, K, BM_l[t], BN_l[t], Algo_l[t], [tiles - 1, 1] if tiles > 1 else [1], [],
-                          comm_op, dtype, warmup=10, reps=reps, raster_group=rg, reduce_group=g)
+    for est, t, rg in ranked[:top_k]:
+        ms = _fused_time(impl, M, N, K, BM_l[t], BN_l[t], Algo_l[t], comm_op, dtype, rg, reps)
         if rank == 0 and verbose:
-            print(f"Algo {Algo_l[t]} raster {rg} reduce {g}: predicted {est:.4f} ms, measured {ms:.4f} ms")
+            print(f"Algo {Algo_l[t]} raster {rg}: predicted {est:.4f} ms, measured {ms:.4f} ms")
         if best is None or ms < best[0]:
-            best = (ms, t, rg, g, est)
-    ms, t, rg, g, est = best
+            best = (ms, t, rg, est)
+    ms, t, rg, est = best
     _, hint = find_hint(impl, M, N, K, BM_l[t:t + 1], BN_l[t:t + 1], Algo_l[t:t + 1], comm_op, dtype)
+    # grouping: predicted on the measured curve, then the pick is timed (reference: tune/search.py:529-596)
+    cseg, seg_ms, timed = search_two_stream(impl, M, N, K, Algo_l[t], comm_op, dtype, curve=curve, gemm_ms=dur_l[t],
+                                            top_k=1, reps=seg_reps, hint=hint)
     tiles = div_up(M, BM_l[t]) * div_up(N, BN_l[t])
-    cseg, seg_ms = best_segmentation(M, N, dur_l[t], curve, tiles, comm_op, ws, sm_count() // (BM_l[t] // 128), 0)
+    _, seg_pred = best_segmentation(M, N, dur_l[t], curve, tiles, comm_op, ws, sm_count() // (BM_l[t] // 128), 16)
     sol = dict(BM=BM_l[t], BN=BN_l[t], dur=dur_l[t], Algo=Algo_l[t], hint=hint, cSeg=cseg, raster_group=rg,
-               reduce_group=g, fused_dur=ms, predicted_dur=est, segmented_model_dur=seg_ms, comm_op=comm_op,
-               world_size=ws, search="predictive")
+               fused_dur=ms, predicted_dur=est, two_stream_dur=seg_ms, segmented_model_dur=seg_pred,
+               candidates_timed=len(timed), comm_op=comm_op, world_size=ws, search="predictive")
     if rank == 0:
         cfg.save_stage2(M, N, K, path=path, **sol)
         if verbose:

@@ -20,8 +20,8 @@ from typing import Optional, Sequence
 
 import torch
 
-# Tile table of the native library (csrc/kernels/gemm_launch.h), index = Algo.
-ALGO_TILES = [(128, 256, 64), (128, 128, 64), (128, 64, 64), (256, 256, 64), (256, 128, 64)]
+# Tile table of the native library, index = Algo (written by tool/generate_instances.py).
+from ._algo_table import ALGO_TILES  # noqa: E402
 
 REPO_ROOT = Path(__file__).resolve().parents[2]
 

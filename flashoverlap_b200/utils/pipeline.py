@@ -1,10 +1,12 @@
-"""Double-buffered host-to-device input feeder.
+"""Double-buffered host-to-device input feeder and device-to-host result reader.
 
 A serving loop that receives every step's activations from the host pays the
 PCIe copy on the critical path unless the copy of step i+1 runs while step i
-computes.  ``HostFeeder`` keeps two device buffers and a copy stream: ``next()``
-returns the device tensor holding the batch submitted one call earlier and
-starts the copy of the batch passed now."""
+computes.  ``HostFeeder`` keeps two device buffers and a copy stream: ``take()``
+returns the device tensor holding the batch submitted last and ``submit()``
+starts the copy of the next one.  ``ResultReader`` does the same in the other
+direction: the result of step i travels to pinned host memory while step i+1
+computes."""
 from __future__ import annotations
 
 from typing import Optional
@@ -44,3 +46,49 @@ class HostFeeder:
         s = 0 if slot_tensor.data_ptr() == self.bufs[0].data_ptr() else 1
         self.consumed[s].record(torch.cuda.current_stream())
         self.primed = True
+
+
+class ResultReader:
+    """Copies every step's result into one of two pinned host buffers on a
+    copy stream of its own.
+
+    The fused all-reduce returns a tensor that aliases one of two alternating
+    symmetric result buffers, so the copy of step i must have finished before
+    step i+2 overwrites that buffer: call ``before_step()`` before launching a
+    step, ``fetch(result)`` after it, and ``wait_all()`` before reading the
+    host buffers."""
+
+    def __init__(self, shape, dtype, device=None):
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(2)]
+        self.done = [torch.cuda.Event(), torch.cuda.Event()]
+        self.produced = torch.cuda.Event()
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        self.slot = 0
+        self.used = [False, False]
+
+    def before_step(self) -> None:
+        """The step about to be launched may overwrite the device buffer that the
+        copy issued two steps ago reads: make the current stream wait for it."""
+        if self.used[self.slot]:
+            torch.cuda.current_stream().wait_event(self.done[self.slot])
+
+    def fetch(self, result: torch.Tensor) -> torch.Tensor:
+        """Start copying ``result`` to the host once the work enqueued so far on
+        the current stream is done.  Returns the host buffer it will land in."""
+        s = self.slot
+        if self.used[s]:
+            self.done[s].synchronize()  # the host buffer still holds the result of two steps ago
+        self.produced.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.produced)
+            self.host[s].copy_(result, non_blocking=True)
+            self.done[s].record(self.copy_stream)
+        self.used[s] = True
+        self.slot ^= 1
+        return self.host[s]
+
+    def wait_all(self) -> None:
+        for s in range(2):
+            if self.used[s]:
+                self.done[s].synchronize()

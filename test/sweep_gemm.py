@@ -6,7 +6,14 @@ tile configuration per shape) against the vendor GEMM over an M x N x K grid.
 import argparse
 import json
 
-from _common import DTYPES, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES  # noqa: E402
 
 from flashoverlap_b200.tune.runtime import make_inputs, mean_time_ms, usable_algos
 from flashoverlap_b200.utils import config as cfg

@@ -1,18 +1,53 @@
-"""Shape sweep of the fused operations against the non-overlapped baseline
-(cuBLAS GEMM, one NCCL collective, RMSNorm kernel) at the tensor-parallel size
-of this job: M in {1024..16384}, N in {4096, 8192}, K in {4096, 8192, 14336}
-split over the ranks, fp16 by default.  Steps of both sides alternate, the L2
-is flushed before every step, times are the MAX over ranks.
+"""Shape sweep of the fused operations at the tensor-parallel size of this job,
+with the exhaustive and the predictive search run side by side on every shape:
+M in {1024..16384}, N in {4096, 8192}, K in {4096, 8192, 14336} split over the
+ranks, fp16 by default (the sweep the reference's predictive search is meant
+for; reference: tune/search.py:529-618).
 
-    torchrun --nproc_per_node=8 test/sweep_overlap.py [--m_list 1024 4096] [--jsonl sweep.jsonl]
+For every shape and both collectives the script
+
+1. times this library's GEMM for the candidate tile configurations (stage 1),
+2. exhaustive: times the fused kernel for every (tile configuration, raster
+   group) candidate and keeps the best,
+3. predictive: ranks the same candidates with the cost model on the link
+   bandwidth MEASURED at the start of the run (the library's own transport, 64 MiB
+   messages) and times only the model's first pick,
+4. times the non-overlapped baseline (cuBLAS GEMM, one NCCL collective, RMSNorm
+   kernel) in alternation with the best fused configuration.
+
+Times are the MAX over ranks, L2 flushed before every timed step.
+
+    torchrun --nproc_per_node=8 test/sweep_overlap.py [--m_list 1024 4096] [--jsonl sweep.jsonl] [--md sweep.md]
 """
 import argparse
 import json
+import os
+import sys
 
-from _common import DTYPES, finish, make_baseline_impl, make_overlap_impl, start, torch
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from flashoverlap_b200.parallel import max_over_ranks
-from flashoverlap_b200.utils.timing import time_pairs
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES, finish, make_baseline_impl, make_overlap_impl, start  # noqa: E402
+from flashoverlap_b200.parallel import max_over_ranks  # noqa: E402
+from flashoverlap_b200.tune.model import predict_fused_ms  # noqa: E402
+from flashoverlap_b200.tune.runtime import mean_time_ms  # noqa: E402
+from flashoverlap_b200.tune.search import knob_candidates  # noqa: E402
+from flashoverlap_b200.utils.config import ALGO_TILES  # noqa: E402
+from flashoverlap_b200.utils.timing import time_pairs  # noqa: E402
+
+
+def measure_link(impl, ws, reps=10):
+    """(GB/s per NVLink direction per GPU, "nvls" | "p2p") of the transport the fused kernels use."""
+    if ws == 1:
+        return 1.0, "p2p"
+    total = 64 << 20
+    if impl.nvls_available():
+        ms = mean_time_ms(lambda: impl.multimem_bench("allreduce", total, 0, False), 3, reps)
+        return total * (1 + 1 / ws) / (ms * 1e-3) / 1e9, "nvls"
+    per_peer = total // (ws - 1) // 16 * 16
+    ms = mean_time_ms(lambda: impl.p2p_push(per_peer, 0), 3, reps)
+    return per_peer * (ws - 1) / (ms * 1e-3) / 1e9, "p2p"
 
 
 def main():
@@ -22,19 +57,25 @@ def main():
     ap.add_argument("--k_list", type=int, nargs="+", default=[4096, 8192, 14336], help="K before the split")
     ap.add_argument("--dtype", default="float16", choices=sorted(DTYPES))
     ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--search_reps", type=int, default=5)
+    ap.add_argument("--algos", type=int, nargs="+", default=[0, 3, 4], help="tile configurations to consider")
     ap.add_argument("--jsonl", default=None)
+    ap.add_argument("--md", default=None, help="write a markdown table here (rank 0)")
     args = ap.parse_args()
     rank, ws = start()
     dt = DTYPES[args.dtype]
     impl = make_overlap_impl(max_m=max(args.m_list), max_n=max(args.n_list))
     base = make_baseline_impl()
+    link_gbs, link_kind = measure_link(impl, ws)
+    rows_md = []
     if rank == 0:
-        print(f"TP={ws} {args.dtype}\n{'M':>6} {'N':>6} {'K/rank':>7} | {'AR fused':>9} {'AR base':>9} {'x':>5} | "
-              f"{'RS fused':>9} {'RS base':>9} {'x':>5}   (ms, with RMSNorm)")
+        print(f"TP={ws} {args.dtype}; measured link {link_gbs:.0f} GB/s per direction ({link_kind})")
+        print(f"{'op':>3} {'M':>6} {'N':>6} {'K/rank':>7} | {'exh ms':>8} {'pick':>10} | {'pred ms':>8} {'pick':>10} "
+              f"{'gap':>6} | {'base ms':>8} {'x':>5}")
+    agree = total = 0
     for M in args.m_list:
         if M % ws or (M // ws) % 128:
             continue
-        algo = 3 if M % 256 == 0 else 0
         for N in args.n_list:
             for Kt in args.k_list:
                 K = Kt // ws // 8 * 8
@@ -45,29 +86,76 @@ def main():
                 O = torch.empty_like(C)
                 D = torch.empty(M // ws, N, device="cuda", dtype=dt)
                 DO = torch.empty_like(D)
+                algos = [a for a in args.algos if M % ALGO_TILES[a][0] == 0 and N % ALGO_TILES[a][1] == 0
+                         and (M // ws) % ALGO_TILES[a][0] == 0]
+                gemm_ms = {a: mean_time_ms(lambda a=a: impl.cutlass_gemm(A, B, C, a), 3, args.search_reps, flush=True)
+                           for a in algos}
+                for op in ("all_reduce", "reduce_scatter"):
+                    def fused(a):
+                        if op == "all_reduce":
+                            impl.gemm_allreduce_fused(A, B, W, 1e-5, a)
+                        else:
+                            impl.gemm_reducescatter_fused(A, B, D, W, 1e-5, a, False)
 
-                def b_ar():
-                    base.gemm_allreduce(A, B, C)
-                    torch.ops.flashoverlap_op.rmsnorm(C, O, W, 1e-5)
+                    def timed(a, rg):
+                        impl.set_raster_group(rg)
+                        try:
+                            return mean_time_ms(lambda: fused(a), 3, args.search_reps, flush=True)
+                        finally:
+                            impl.set_raster_group(0)
 
-                def b_rs():
-                    base.gemm_reducescatter(A, B, C, D)
-                    torch.ops.flashoverlap_op.rmsnorm(D, DO, W, 1e-5)
+                    cands = [(a, rg) for a in algos for rg in knob_candidates(M, ALGO_TILES[a][0])]
+                    times = {c: timed(*c) for c in cands}                       # exhaustive: everything is timed
+                    ex = min(times, key=times.get)
+                    kind = link_kind if op == "all_reduce" else "p2p"
+                    pred = {c: predict_fused_ms(M, N, gemm_ms[c[0]], ws, op, link_gbs, transport=kind,
+                                                tile_m=ALGO_TILES[c[0]][0], raster_group=c[1]) for c in cands}
+                    pr = min(pred, key=pred.get)
+                    pr_ms = timed(*pr)                                          # predictive: only its pick is timed
+                    gap = pr_ms / times[ex] - 1.0
 
-                f1, b1 = time_pairs(lambda: impl.gemm_allreduce_fused(A, B, W, 1e-5, algo), b_ar, args.steps, 3)
-                f2, b2 = time_pairs(lambda: impl.gemm_reducescatter_fused(A, B, D, W, 1e-5, algo, False), b_rs,
-                                    args.steps, 3)
-                t = [max_over_ranks(sum(x)) / args.steps for x in (f1, b1, f2, b2)]
-                impl.check_status()
-                if rank == 0:
-                    print(f"{M:>6} {N:>6} {K:>7} | {t[0]:>9.4f} {t[1]:>9.4f} {t[1] / t[0]:>5.2f} | {t[2]:>9.4f} "
-                          f"{t[3]:>9.4f} {t[3] / t[2]:>5.2f}", flush=True)
-                    if args.jsonl:
-                        with open(args.jsonl, "a") as fh:
-                            fh.write(json.dumps({"tp": ws, "dtype": args.dtype, "M": M, "N": N, "K_per_rank": K,
-                                                 "ar_fused_ms": t[0], "ar_baseline_ms": t[1], "rs_fused_ms": t[2],
-                                                 "rs_baseline_ms": t[3]}) + "\n")
+                    def b_step():
+                        if op == "all_reduce":
+                            base.gemm_allreduce(A, B, C)
+                            torch.ops.flashoverlap_op.rmsnorm(C, O, W, 1e-5)
+                        else:
+                            base.gemm_reducescatter(A, B, C, D)
+                            torch.ops.flashoverlap_op.rmsnorm(D, DO, W, 1e-5)
+
+                    impl.set_raster_group(ex[1])
+                    f, b = time_pairs(lambda: fused(ex[0]), b_step, args.steps, 3)
+                    impl.set_raster_group(0)
+                    f_ms, b_ms = max_over_ranks(sum(f)) / args.steps, max_over_ranks(sum(b)) / args.steps
+                    impl.check_status()
+                    total += 1
+                    agree += int(gap <= 0.05)
+                    rec = {"tp": ws, "dtype": args.dtype, "op": op, "M": M, "N": N, "K_per_rank": K,
+                           "exhaustive": {"algo": ex[0], "raster": ex[1], "ms": times[ex], "timed": len(cands)},
+                           "predictive": {"algo": pr[0], "raster": pr[1], "ms": pr_ms, "predicted_ms": pred[pr],
+                                          "timed": 1}, "gap": gap, "fused_ms": f_ms, "baseline_ms": b_ms,
+                           "speedup": b_ms / f_ms, "link_gbs": link_gbs, "link_kind": kind}
+                    if rank == 0:
+                        tag = "AR" if op == "all_reduce" else "RS"
+                        print(f"{tag:>3} {M:>6} {N:>6} {K:>7} | {times[ex]:>8.4f} {str(ex):>10} | {pr_ms:>8.4f} "
+                              f"{str(pr):>10} {100 * gap:>5.1f}% | {b_ms:>8.4f} {b_ms / f_ms:>5.2f}", flush=True)
+                        rows_md.append(f"| {tag} | {M} | {N} | {K} | {times[ex]:.4f} | Algo {ex[0]} raster {ex[1]} | "
+                                       f"{pr_ms:.4f} | Algo {pr[0]} raster {pr[1]} | {100 * gap:.1f} % | {f_ms:.4f} | "
+                                       f"{b_ms:.4f} | {b_ms / f_ms:.2f} |")
+                        if args.jsonl:
+                            with open(args.jsonl, "a") as fh:
+                                fh.write(json.dumps(rec) + "\n")
                 del A, B, C, O, D, DO
+    if rank == 0:
+        summary = (f"predictive pick within 5 % of the exhaustive best on {agree} of {total} cases "
+                   f"({100.0 * agree / max(total, 1):.0f} %)")
+        print(summary)
+        if args.md:
+            with open(args.md, "w") as fh:
+                fh.write(f"TP = {ws}, {args.dtype}, link {link_gbs:.0f} GB/s per direction ({link_kind}, measured at "
+                         f"the start of the run); times in ms, MAX over ranks, RMSNorm included.\n\n")
+                fh.write("| op | M | N | K/rank | exhaustive ms | pick | predictive ms | pick | gap | fused | "
+                         "cuBLAS+NCCL+RMSNorm | speed-up |\n|---|---|---|---|---|---|---|---|---|---|---|---|\n")
+                fh.write("\n".join(rows_md) + "\n\n" + summary + "\n")
     finish()
 
 

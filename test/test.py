@@ -11,18 +11,22 @@ time and writes one JSON line per run (``--jsonl``).
 import argparse
 import json
 
-from _common import DTYPES, finish, make_baseline_impl, make_overlap_impl, start, torch
+import os
+import sys
 
-from flashoverlap_b200.tune.model import div_up
-from flashoverlap_b200.tune.runtime import make_inputs, mean_time_ms
-from flashoverlap_b200.utils import config as cfg
-from flashoverlap_b200.utils.reorder import generate_row_mapping, reorder_indices
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-PEAK_TFLOPS = 1629.4   # measured cuBLAS bf16 burst on this pool
-LINK_GBS = 770.0       # measured peer copy bandwidth per direction
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import (DTYPES, finish, make_baseline_impl, make_overlap_impl, measured_link_gbs,  # noqa: E402
+                                   measured_peaks, start)
+from flashoverlap_b200.tune.model import div_up  # noqa: E402
+from flashoverlap_b200.tune.runtime import make_inputs, mean_time_ms, search_two_stream  # noqa: E402
+from flashoverlap_b200.utils import config as cfg  # noqa: E402
+from flashoverlap_b200.utils.reorder import generate_row_mapping, reorder_indices  # noqa: E402
 
 
-def main():
+def build_parser():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m_dim", "--m", type=int, default=4096)
     ap.add_argument("--k_dim", "--k", type=int, default=8192)
@@ -34,8 +38,13 @@ def main():
     ap.add_argument("--reps", type=int, default=200)
     ap.add_argument("--path", default=None)
     ap.add_argument("--jsonl", default=None)
-    args = ap.parse_args()
-    rank, ws = start()
+    ap.add_argument("--peaks", default=None, help="JSON file with the measured peaks (default: MEASURED_PEAKS.json)")
+    return ap
+
+
+def main(argv=None, rendezvous_retries=0):
+    args = build_parser().parse_args(argv)
+    rank, ws = start(retries=rendezvous_retries)
     M, N, K = args.m_dim, args.n_dim, args.k_dim
     dtype = DTYPES[args.dtype]
     try:
@@ -52,7 +61,6 @@ def main():
     cseg = [(M // BM) * (N // BN)] if args.single_seg else sol["cSeg"]
     impl, base = make_overlap_impl(), make_baseline_impl()
     impl.set_raster_group(int(sol.get("raster_group", 0)))
-    impl.set_reduce_group(int(sol.get("reduce_group", 0)))
     A, B, C = make_inputs(M, N, K, dtype)
     W = torch.empty(N, dtype=dtype, device="cuda").normal_(1.0, 0.1)
     D = torch.empty((M // ws, N), dtype=dtype, device="cuda")
@@ -103,12 +111,16 @@ def main():
         if args.rmsnorm:
             torch.ops.flashoverlap_op.reorder_rmsnorm(C if ar else D, O, W, BM if ar else BM // ws, BN, 1, RA)
 
-    # the reference's own design on this machine: wave groups of (SMs - 16) tiles
-    ctas_per_tile = BM // 128
-    wave = max(1, (torch.cuda.get_device_properties(0).multi_processor_count - 16) // ctas_per_tile)
+    # The reference's own design on this machine, with the wave grouping its
+    # search found for this shape (the tuned file's cSeg) or, without a tuned
+    # file, the best of a quick timed search over compositions of <= 4 units.
     tiles = tm * tn
-    groups = [min(wave, tiles - i) for i in range(0, tiles, wave)]
-    if len(groups) >= tn:
+    if "two_stream_dur" in sol and sum(sol["cSeg"]) == tiles and len(sol["cSeg"]) < tn:
+        groups = list(sol["cSeg"])
+    elif ws > 1:
+        groups, _, _ = search_two_stream(impl, M, N, K, algo, args.comm_op, dtype, max_units=4, warmup=3, reps=10,
+                                         hint=sol["hint"])
+    else:
         groups = [tiles]
     cs2_cpu = torch.tensor(groups, dtype=torch.int32)
     cs2_gpu = cs2_cpu.cuda()
@@ -118,9 +130,22 @@ def main():
     t_base = mean_time_ms(baseline, 20, r)
     t_over = mean_time_ms(overlap, 20, r)
     impl.check_status()
+    # roofline: the slower of the GEMM at the measured peak and the bytes one GPU must move per NVLink direction
+    # at the measured link bandwidth; both numbers come from measurement files, none is typed in here
     flop = 2.0 * M * N * K
-    out_bytes = M * N * A.element_size() * (ws - 1) / ws * (2 if ar else 1)
-    roof_ms = max(flop / (PEAK_TFLOPS * 1e12), out_bytes / (LINK_GBS * 1e9)) * 1e3
+    peaks = measured_peaks(args.peaks)
+    link_gbs, link_src = measured_link_gbs(ws, path=args.path)
+    nvls = impl.nvls_available()
+    S = M * N * A.element_size()
+    if ws == 1:
+        out_bytes = 0.0
+    elif ar:
+        out_bytes = S * (1 + 1 / ws) if nvls else 2 * S * (ws - 1) / ws
+    else:
+        out_bytes = S * (ws - 1) / ws
+    roof_ms = None
+    if peaks.get("bf16_tflops") and (ws == 1 or link_gbs):
+        roof_ms = max(flop / (peaks["bf16_tflops"] * 1e12), out_bytes / (link_gbs * 1e9) if ws > 1 else 0.0) * 1e3
     if rank == 0:
         print(f"M={M} N={N} K={K} (per rank) TP={ws} {args.dtype} comm_op={args.comm_op} Algo={algo} cSeg={cseg}")
         print("GEMM dur:        %.4f ms" % t_gemm)
@@ -130,14 +155,19 @@ def main():
         print("overlap dur:     %.4f ms" % t_over)
         print("two-stream dur:  %.4f ms   (reference design: signalling GEMM + stream waits + %d NCCL calls)" % (t_two, len(groups)))
         print("speedup:         %.4f" % (t_base / t_over))
-        print("roofline:        %.4f ms -> fused reaches %.1f %% of it" % (roof_ms, 100 * roof_ms / t_over))
+        if roof_ms is not None:
+            print("roofline:        %.4f ms -> fused reaches %.1f %% of it (of measured: %.0f TFLOP/s, %s GB/s from %s)"
+                  % (roof_ms, 100 * roof_ms / t_over, peaks["bf16_tflops"], link_gbs, link_src or "-"))
+        else:
+            print("roofline:        not computed (no measured peaks / link curve found)")
         if args.jsonl:
             with open(args.jsonl, "a") as fh:
                 fh.write(json.dumps({"M": M, "N": N, "K": K, "tp": ws, "dtype": args.dtype, "comm_op": args.comm_op,
                                      "rmsnorm": args.rmsnorm, "single_seg": args.single_seg, "algo": algo,
                                      "gemm_ms": t_gemm, "vendor_gemm_ms": t_vendor, "comm_ms": t_comm,
                                      "baseline_ms": t_base, "overlap_ms": t_over, "two_stream_ms": t_two, "speedup": t_base / t_over,
-                                     "roofline_ms": roof_ms, "roofline_frac": roof_ms / t_over}) + "\n")
+                                     "two_stream_cseg": groups, "roofline_ms": roof_ms,
+                                     "roofline_frac": (roof_ms / t_over) if roof_ms else None}) + "\n")
     finish()
 
 

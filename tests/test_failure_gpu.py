@@ -24,12 +24,15 @@ def test_wait_that_nothing_satisfies_times_out_with_status():
     assert st[0] == 2 and st[4] == 1, impl.status_string()  # ST_TIMEOUT_FLAG, wanted 1
     with pytest.raises(RuntimeError, match="did not arrive"):
         impl.check_status()
-    impl.reset()
-    assert impl.status()[0] == 0
-    # the context is still usable
+    # the next operation refuses to run on top of a reported failure, without anybody asking for the status
     A = torch.randn(256, 128, device="cuda", dtype=torch.float16)
     B = torch.randn(256, 128, device="cuda", dtype=torch.float16)
     C = torch.empty(256, 256, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="earlier flashoverlap kernel reported a failure"):
+        impl.cutlass_gemm(A, B, C, 0)
+    impl.reset()
+    assert impl.status()[0] == 0
+    # the context is still usable
     impl.cutlass_gemm(A, B, C, 0)
     torch.cuda.synchronize()
     impl.check_status()

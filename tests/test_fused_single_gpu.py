@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import flashoverlap_b200  # noqa: F401
+from flashoverlap_b200.utils.config import ALGO_TILES
 from flashoverlap_b200.utils.reorder import from_tile_order, reorder_indices, to_tile_order
 
 pytestmark = pytest.mark.gpu
@@ -34,7 +35,7 @@ def make_inputs(M, N, K, dtype, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("algo", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("algo", list(range(len(ALGO_TILES))))
 def test_gemm_rmsnorm_single_kernel(dtype, algo):
     M, N, K = 1024, 4096, 512
     A, B, W = make_inputs(M, N, K, dtype)
@@ -50,6 +51,58 @@ def test_gemm_rmsnorm_single_kernel(dtype, algo):
     want = rms_ref(C, W, 1e-5)  # the kernel normalises the 16-bit product it stored
     assert torch.isfinite(O.float()).all()
     assert (O.float() - want).abs().max().item() <= tol * want.abs().max().item()
+
+
+@pytest.mark.parametrize("N", [512, 2304, 8192, 16384, 16640])
+def test_gemm_rmsnorm_row_widths(N):
+    # rows that fill a fraction of the row group's registers (512), that end inside a
+    # warp's chunk range (2304), that fill them exactly (8192), and wide rows
+    # that take the two-pass path (16384, 16640)
+    M, K = 256, 128
+    A, B, W = make_inputs(M, N, K, torch.float16, seed=N)
+    C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    O = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float16)
+    impl = make_impl()
+    impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, 0)
+    torch.cuda.synchronize()
+    impl.check_status()
+    want = rms_ref(C, W, 1e-5)
+    assert torch.isfinite(O.float()).all()
+    assert (O.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_gemm_rmsnorm_more_rows_than_one_wave():
+    # 8192 rows: every row group takes many rows; the GEMM warps join the reduce phase
+    M, N, K = 8192, 2048, 256
+    A, B, W = make_inputs(M, N, K, torch.bfloat16, seed=21)
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    O = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    impl = make_impl()
+    for _ in range(2):
+        impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, 3)
+    torch.cuda.synchronize()
+    impl.check_status()
+    want = rms_ref(C, W, 1e-5)
+    assert torch.isfinite(O.float()).all()
+    assert (O.float() - want).abs().max().item() <= 3e-2 * want.abs().max().item()
+
+
+def test_phase_trace_records_every_row_once():
+    M, N, K = 2048, 2048, 256
+    A, B, W = make_inputs(M, N, K, torch.float16, seed=4)
+    C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    O = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    impl = make_impl()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    trace = torch.zeros(8 * sms, dtype=torch.int64, device="cuda")
+    impl.set_phase_trace(trace)
+    impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, 0)
+    torch.cuda.synchronize()
+    impl.set_phase_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
+    t = trace.view(sms, 8).cpu()
+    assert int(t[:, 5].sum()) == M            # rows reduced, over all CTAs
+    assert int(t[:, 3].sum()) == (M // 128) * (N // 256)  # tiles computed
+    assert bool((t[:, 1] >= t[:, 0]).all())   # GEMM phase ends after the start
 
 
 @pytest.mark.parametrize("with_norm", [False, True])
@@ -102,6 +155,31 @@ def test_compat_overlap_api_reordered_layout_and_trace():
     torch.cuda.synchronize()
     want = rms_ref(got, W, 1e-5)
     assert (out.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+
+
+def test_index_arrays_are_checked_on_the_host_before_any_launch():
+    M, N, K, algo = 256, 512, 64, 0
+    A, B, W = make_inputs(M, N, K, torch.float16)
+    impl = make_impl()
+    MM = torch.zeros((1, 2), dtype=torch.int32, device="cuda")
+    C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    cseg = torch.tensor([4], dtype=torch.int32)
+    out_of_range = torch.tensor([[0, 1], [2, 400]], dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="outside"):
+        impl.gemm_allreduce_overlap(A, B, C, MM, out_of_range, 1, cseg, cseg.cuda(), algo, False)
+    duplicate = torch.tensor([[0, 1], [1, 3]], dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="permutation"):
+        impl.gemm_allreduce_overlap(A, B, C, MM, duplicate, 1, cseg, cseg.cuda(), algo, False)
+    with pytest.raises(RuntimeError, match="outside"):
+        torch.ops.flashoverlap_op.reorder_rmsnorm(C, torch.empty_like(C), W, 128, 256, 1, out_of_range)
+    # a tensor that passed the check is checked again after it has been written to
+    RA = reorder_indices(4, [], device="cuda").reshape(2, 2)
+    impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg, cseg.cuda(), algo, False)
+    RA[1, 1] = 77
+    with pytest.raises(RuntimeError, match="outside"):
+        impl.gemm_allreduce_overlap(A, B, C, MM, RA, 1, cseg, cseg.cuda(), algo, False)
+    torch.cuda.synchronize()
+    impl.check_status()
 
 
 def test_compat_overlap_api_rejects_bad_segments():

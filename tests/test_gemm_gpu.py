@@ -3,6 +3,9 @@ import pytest
 import torch
 
 import flashoverlap_b200  # noqa: F401  (registers the classes)
+from flashoverlap_b200.utils.config import ALGO_TILES
+
+ALGOS = list(range(len(ALGO_TILES)))
 
 pytestmark = pytest.mark.gpu
 
@@ -19,13 +22,13 @@ def _ref(A, B):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("algo", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (512, 1024, 1000), (1024, 2048, 4096)])
 def test_gemm_matches_fp32_reference(dtype, algo, shape):
     M, N, K = shape
     K = (K + 7) // 8 * 8
-    if algo >= 3 and M % 256:
-        pytest.skip("CTA-pair tiles are 256 rows tall")
+    if M % ALGO_TILES[algo][0] or N % ALGO_TILES[algo][1]:
+        pytest.skip("shape is not a multiple of this tile")
     torch.manual_seed(0)
     A = torch.randn(M, K, device="cuda", dtype=dtype)
     B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(dtype)
@@ -49,7 +52,7 @@ def test_gemm_many_tiles_persistent_loop():
     B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
     C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     impl = _impl()
-    for algo in (0, 1, 2, 3, 4):
+    for algo in ALGOS:
         C.fill_(float("nan"))
         impl.cutlass_gemm(A, B, C, algo)
         torch.cuda.synchronize()
@@ -82,3 +85,9 @@ def test_gemm_rejects_bad_shapes():
         impl.cutlass_gemm(A, B, C, 0)
     with pytest.raises(RuntimeError):
         impl.cutlass_gemm(A.float(), B.float(), C.float(), 0)
+
+
+def test_algo_table_matches_generated_python_copy():
+    impl = _impl()
+    assert impl.num_algos() == len(ALGO_TILES)
+    assert [tuple(impl.algo_tile(a)) for a in ALGOS] == [tuple(t) for t in ALGO_TILES]

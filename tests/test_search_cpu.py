@@ -7,13 +7,17 @@ import json
 import pytest
 import torch
 
-from flashoverlap_b200.tune import search
+import types
+
+from flashoverlap_b200.tune import runtime, search
 from flashoverlap_b200.utils import config as cfg
 
 
-def fake_time(algo, raster, reduce_group):
-    # Algo 3 fastest, raster 2 and the automatic reduce group best
-    return 0.2 + 0.01 * abs(algo - 3) + 0.002 * abs(raster - 2) + 0.001 * reduce_group
+def fake_time(algo, raster, cseg, two_stream):
+    # fused path: Algo 3 fastest, raster 2 best; two-stream path: three groups best
+    if two_stream:
+        return 0.5 + 0.02 * abs(len(cseg) - 3) + 0.001 * abs(cseg[0] - cseg[-1]) / max(cseg)
+    return 0.2 + 0.01 * abs(algo - 3) + 0.002 * abs(raster - 2)
 
 
 @pytest.fixture
@@ -21,15 +25,19 @@ def patched(monkeypatch, tmp_path):
     calls = []
 
     def perf_running(impl, M, N, K, BM, BN, algo, cseg, hint, comm_op, dtype=None, warmup=0, reps=0, raster_group=0,
-                     reduce_group=0):
-        calls.append((algo, raster_group, reduce_group))
-        return fake_time(algo, raster_group, reduce_group)
+                     two_stream=False, gemm_ctas=0):
+        calls.append((algo, raster_group, tuple(cseg), two_stream))
+        return fake_time(algo, raster_group, list(cseg), two_stream)
 
     def compute_hint(impl, M, N, K, BM, BN, algo, wave, comm_op, dtype=None, **kw):
         tiles = (M // BM) * (N // BN)
         return True, list(reversed(range(tiles)))
 
     monkeypatch.setattr(search, "perf_running", perf_running)
+    monkeypatch.setattr(runtime, "perf_running", perf_running)
+    monkeypatch.setattr(runtime, "world", lambda: (0, 8))
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda *a, **k: types.SimpleNamespace(multi_processor_count=148))
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
     monkeypatch.setattr(search, "compute_hint", compute_hint)
     monkeypatch.setattr(search, "sm_count", lambda: 148)
     monkeypatch.setattr(search, "world", lambda: (0, 8))
@@ -43,12 +51,17 @@ def test_exhaustive_and_predictive_agree(patched):
     calls, path, (M, N, K) = patched
     ex = search.exhaustive_search(None, M, N, K, "all_reduce", path=path, verbose=False)
     n_exhaustive = len(calls)
-    assert ex["Algo"] == 3 and ex["raster_group"] == 2 and ex["reduce_group"] == 0
+    assert ex["Algo"] == 3 and ex["raster_group"] == 2
+    # the wave grouping was searched by timing compositions on the two-stream path
+    timed_groupings = {c[2] for c in calls if c[3]}
+    assert len(timed_groupings) == ex["candidates_timed"] > 4
+    assert len(ex["cSeg"]) == 3 and ex["two_stream_dur"] == min(fake_time(3, 0, list(g), True) for g in timed_groupings)
     # re-running from the stage-2 file works because the stage-1 lists are kept
     calls.clear()
     curve = torch.tensor([[2.0 ** 20, 150.0], [2.0 ** 26, 420.0]])
     pr = search.predictive_search(None, M, N, K, "all_reduce", curve, 550.0, path=path, verbose=False)
-    assert len(calls) <= 3 < n_exhaustive
+    assert len([c for c in calls if not c[3]]) <= 3 and len(calls) < n_exhaustive
+    assert len([c for c in calls if c[3]]) == 1  # the predicted grouping is timed once
     assert (pr["Algo"], pr["raster_group"]) == (ex["Algo"], ex["raster_group"])
     data = json.load(open(cfg.json_path(M, N, K, path)))
     cfg.validate_stage2(data, M, N)
@@ -65,5 +78,12 @@ def test_search_fails_loudly_without_consistent_hint(patched, monkeypatch):
 
 
 def test_knob_candidates_cover_defaults():
-    c = search.knob_candidates(4096, 8)
-    assert (2, 0) in c and (1, 1) in c and all(rg in search.RASTER_CHOICES for rg, _ in c)
+    assert search.knob_candidates(4096, 256) == [1, 2, 4, 8]
+    assert search.knob_candidates(512, 256) == [1, 2]
+
+
+def test_predictive_search_needs_a_measured_link_bandwidth(patched):
+    calls, path, (M, N, K) = patched
+    curve = torch.tensor([[2.0 ** 20, 150.0], [2.0 ** 26, 420.0]])
+    with pytest.raises(ValueError, match="measured link bandwidth"):
+        search.predictive_search(None, M, N, K, "all_reduce", curve, None, path=path, verbose=False)

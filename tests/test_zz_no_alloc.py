@@ -72,6 +72,11 @@ def test_no_alloc_entry_matches_regular_entry_twice(dtype):
         tol = 1e-2 if dtype == torch.float16 else 3e-2
         err = (got.float() - want.float()).abs().max().item()
         assert err <= tol * max(1.0, want.float().abs().max().item()), f"call {call}: max abs err {err}"
+        # and against plain PyTorch in fp32
+        ref = A.float() @ B.float().t()
+        ref = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + eps) * W.float()
+        err32 = (got.float() - ref).abs().max().item()
+        assert err32 <= 2 * tol * max(1.0, ref.abs().max().item()), f"call {call}: max abs err vs fp32 {err32}"
 
 
 def test_no_alloc_entry_rejects_oversized_and_misshapen_problems():
@@ -90,4 +95,8 @@ def test_no_alloc_entry_rejects_oversized_and_misshapen_problems():
     rc = fn(A.data_ptr(), B.data_ptr(), W.data_ptr(), out.data_ptr(), 100, 256, 64, 0, 1e-5, stream, None, err,
             len(err))
     assert rc != 0 and b"M % 128" in err.value
+    # a misaligned operand is refused before anything is enqueued
+    rc = fn(A.data_ptr() + 2, B.data_ptr(), W.data_ptr(), out.data_ptr(), 128, 256, 56, 0, 1e-5, stream, None, err,
+            len(err))
+    assert rc != 0 and b"aligned" in err.value
     torch.cuda.synchronize()

@@ -11,7 +11,14 @@ that waits for other ranks does not survive.)
 """
 import argparse
 
-from _common import DTYPES, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES  # noqa: E402
 
 
 def main():

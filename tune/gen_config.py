@@ -9,30 +9,48 @@ library's kernel.
 import argparse
 import os
 
-from _common import DTYPES, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES  # noqa: E402
 
 from flashoverlap_b200.tune.runtime import make_inputs, mean_time_ms
 from flashoverlap_b200.utils import config as cfg
 
 
-def rows_from_csv(path, algo_dict):
-    import pandas as pd
+def rows_from_csv(path, algo_dict, keep: int = 10):
+    """Algo indices of the fastest rows of a profiler CSV, fastest first.
 
-    df = pd.read_csv(path)
-    cols = {c.lower(): c for c in df.columns}
-    need = ["cta_m", "cta_n", "cta_k", "runtime"]
-    for c in need:
-        if c not in cols:
-            raise ValueError(f"{path} lacks the column {c!r}")
-    df = df.sort_values(cols["runtime"])
+    The file needs the columns ``cta_m``, ``cta_n``, ``cta_k`` and ``Runtime``
+    (any case); ``split_k_slices``, if present, must be 1 in every row that is
+    used (reference: tune/gen_config.py:45-47 asserts the same).  Rows whose tile
+    shape this build does not have are skipped."""
+    import csv
+
+    with open(path, newline="") as fh:
+        reader = csv.DictReader(fh)
+        if reader.fieldnames is None:
+            raise ValueError(f"{path} is empty")
+        cols = {c.strip().lower(): c for c in reader.fieldnames}
+        for c in ("cta_m", "cta_n", "cta_k", "runtime"):
+            if c not in cols:
+                raise ValueError(f"{path} lacks the column {c!r}")
+        rows = list(reader)
+    rows.sort(key=lambda r: float(r[cols["runtime"]]))
     picked = []
-    for _, r in df.iterrows():
-        if "split_k_slices" in cols and int(r[cols["split_k_slices"]]) != 1:
+    for r in rows:
+        key = (int(float(r[cols["cta_m"]])), int(float(r[cols["cta_n"]])), int(float(r[cols["cta_k"]])))
+        if key not in algo_dict:
+            continue
+        if "split_k_slices" in cols and int(float(r[cols["split_k_slices"]])) != 1:
             raise AssertionError("split-K configurations are not supported")
-        key = (int(r[cols["cta_m"]]), int(r[cols["cta_n"]]), int(r[cols["cta_k"]]))
-        if key in algo_dict and algo_dict[key] not in picked:
+        if algo_dict[key] not in picked:
             picked.append(algo_dict[key])
-        if len(picked) == 10:
+        if len(picked) == keep:
             break
     return picked
 

@@ -5,7 +5,14 @@ ten fastest (reference: tune/profile_config.py).
 """
 import argparse
 
-from _common import DTYPES, torch
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from flashoverlap_b200.cli import DTYPES  # noqa: E402
 
 from flashoverlap_b200.tune.runtime import profile_gemm
 from flashoverlap_b200.utils import config as cfg
