@@ -98,7 +98,9 @@ def main():
     # random-init weights ~ N(0,1)/sqrt(K); activations ~ N(0,1)/sqrt(K)
     with torch.no_grad():
         layer.weight.copy_((torch.randn(N, K, device=dev) / K ** 0.5).to(dtype))
-        layer.norm_weight.copy_((1 + 0.1 * torch.randn(N, device=dev)).to(dtype))
+        # the RMSNorm weight is replicated: the same values on every rank
+        gw = torch.Generator(device="cpu").manual_seed(4321)
+        layer.norm_weight.copy_((1 + 0.1 * torch.randn(N, generator=gw)).to(dev, dtype))
     x_host = (torch.randn(M, K) / K ** 0.5).to(dtype).pin_memory()
     x = x_host.to(dev)
 
@@ -196,7 +198,7 @@ def main():
                 "l2": "flushed between timed iterations (256 MB write)",
                 "timing": "CUDA events per step, max over ranks",
                 "algo": args.algo,
-                "transport": "NVLS multimem" if impl.nvls_available() else "P2P stores",
+                "transport": "NVLS multimem" if impl.allreduce_uses_nvls() else "P2P stores",
                 "vs_baseline_is": "nccl_baseline_ms / fused_ms, alternating steps (no published B200 number exists)",
             },
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],

@@ -136,6 +136,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("detach_symmetric", &OverlapImpl::DetachSymmetric)
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)
+      .def("allreduce_uses_nvls", &OverlapImpl::AllReduceUsesNvls)
       .def("p2p_push", &OverlapImpl::P2pPush)
       .def("p2p_push_bulk", &OverlapImpl::P2pPushBulk)
       .def("multimem_bench", &OverlapImpl::MultimemBench)
@@ -145,6 +146,8 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_timeout_ms", &OverlapImpl::SetTimeoutMs)
       .def("set_sm_count", &OverlapImpl::SetSmCount)
       .def("set_raster_group", &OverlapImpl::SetRasterGroup)
+      .def("set_l2_hints", &OverlapImpl::SetL2Hints)
+      .def("set_raster_taper", &OverlapImpl::SetRasterTaper)
       .def("set_phase_trace", &OverlapImpl::SetPhaseTrace)
       .def("status", &OverlapImpl::Status)
       .def("status_string", &OverlapImpl::StatusString)

@@ -626,6 +626,7 @@ void OverlapImpl::DetachSymmetric() {
 }
 void OverlapImpl::SetUseNvls(bool allreduce, bool reducescatter) { engine_.set_use_nvls(allreduce, reducescatter); }
 bool OverlapImpl::NvlsAvailable() { return engine_.nvls_available(); }
+bool OverlapImpl::AllReduceUsesNvls() { return engine_.allreduce_uses_nvls(); }
 
 void OverlapImpl::P2pPush(int64_t bytes, int64_t ctas) {
   require_comm("p2p_push");
@@ -666,6 +667,8 @@ void OverlapImpl::SetTimeoutMs(int64_t ms) {
   engine_.set_timeout_ms(ms);
 }
 void OverlapImpl::SetSmCount(int64_t n) { engine_.set_sm_count(static_cast<int>(n)); }
+void OverlapImpl::SetL2Hints(bool on) { engine_.set_l2_hints(on); }
+void OverlapImpl::SetRasterTaper(bool on) { engine_.set_raster_taper(on); }
 void OverlapImpl::SetRasterGroup(int64_t g) { engine_.set_raster_group(static_cast<int>(g)); }
 void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
   if (buf.numel() == 0) {

@@ -88,6 +88,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   void DetachSymmetric();
   void SetUseNvls(bool allreduce, bool reducescatter);
   bool NvlsAvailable();
+  // Whether the fused all-reduce currently takes the NVLink SHARP path.
+  bool AllReduceUsesNvls();
 
   // Collective: all-to-all push of `bytes` per peer with the P2P store kernel
   // (bandwidth tool); `ctas` = 0 uses every SM.
@@ -114,6 +116,10 @@ class OverlapImpl : public torch::CustomClassHolder {
   void SetTimeoutMs(int64_t ms);
   void SetSmCount(int64_t n);
   void SetRasterGroup(int64_t g);
+  // L2 eviction hints on the GEMM's operand loads (default off).
+  void SetL2Hints(bool on);
+  // Shrinking last raster groups in operations with a reduce phase (default on).
+  void SetRasterTaper(bool on);
   // Every following launch records per-CTA phase timestamps into `buf`
   // (int64, at least 8 * SM count entries, layout in FusedParams::phase_trace;
   // an empty tensor turns it off).

@@ -36,6 +36,10 @@ constexpr int kFlagAReady = kMaxTileRows + 8;
 constexpr int kFlagJob = kMaxTileRows + 32;
 constexpr int kFlagWords = kMaxTileRows + 64;
 
+// Rows up to this many values keep their RMSNorm weight vector in shared memory
+// (and their sums in registers); wider rows take the two-pass path.
+constexpr int kGammaSmemValues = 8192;
+
 // Entries (uint64) per CTA of the optional phase trace.
 constexpr int kTraceWords = 8;
 
@@ -92,8 +96,10 @@ struct alignas(64) FusedParams {
   int M, N, K;
   int TM, TN;        // tile grid (BM = 128)
   int raster_group;  // tile rows walked column-major together (L2 reuse of B)
+  int raster_taper;  // 1 = the last groups shrink by halves so that little is left to communicate after the last tile
   int force_full_grid;  // launch the requested number of CTAs even when there are fewer tiles
   int rot;           // first tile row (rotates ranks apart in block-ownership mode)
+  int l2_hints;      // 1 = TMA loads carry L2 eviction hints (A panel kept, B panel streamed)
 
   // ---- GEMM epilogue destination -------------------------------------------
   int own_mode;             // OwnMode

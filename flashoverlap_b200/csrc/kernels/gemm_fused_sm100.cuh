@@ -59,10 +59,11 @@ struct TileTraits {
   static constexpr int EPI_SLAB_BYTES = 32 * 128;  // 32 rows x 64 columns of 16-bit values
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_SLAB_BYTES;
   static constexpr int BAR_BYTES = 512;
+  static constexpr int GAMMA_BYTES = kGammaSmemValues * 2;  // RMSNorm weight vector of rows up to 8192 values
   static constexpr int SMEM_LIMIT = 227 * 1024;
-  static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (SMEM_LIMIT - 1024 - EPI_BYTES - BAR_BYTES - GAMMA_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + GAMMA_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; power of two >= 32
   static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a CTA pair");
@@ -148,14 +149,35 @@ __device__ __forceinline__ uint32_t norm_pack2(float a, float b, float rstd, uin
 
 // Tile order: tile rows are walked in groups of `raster_group`; inside a group
 // the walk is column-major so that one B panel serves the whole group from L2
-// and tile rows still complete early and in order.
+// and tile rows still complete early and in order.  With `raster_taper` the
+// last groups shrink (G, ..., G, G/2, G/4, ..., 1, 1): the rows of a group can
+// only be reduced once the whole group is computed, so the size of the LAST
+// group is what remains to be communicated after the last tile.
 __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_blk, int& n_blk) {
   const int G = p.raster_group;
-  const int per_group = G * p.TN;
-  const int g = t / per_group;
-  const int r = t - g * per_group;
-  const int first = g * G;
-  const int rows_here = (p.TM - first) < G ? (p.TM - first) : G;
+  int first = 0;      // first tile row of the group that holds tile t
+  int rows_here = G;  // tile rows in that group
+  int r = t;          // index of the tile inside the group
+  if (!p.raster_taper) {
+    const int per_group = G * p.TN;
+    const int g = t / per_group;
+    r = t - g * per_group;
+    first = g * G;
+    rows_here = (p.TM - first) < G ? (p.TM - first) : G;
+  } else {
+    // full groups while more than G tile rows remain, then halves
+    int remaining = p.TM;
+    int size = G;
+    while (true) {
+      if (remaining <= size) size = remaining > 1 ? (remaining + 1) / 2 : 1;
+      const int tiles_here = size * p.TN;
+      if (r < tiles_here || remaining == size) break;
+      r -= tiles_here;
+      first += size;
+      remaining -= size;
+    }
+    rows_here = size;
+  }
   const int mb = first + r % rows_here;
   n_blk = r / rows_here;
   m_blk = mb + p.rot;
@@ -165,11 +187,12 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
 // ---------------------------------------------------------------------------
 // reduce phase: groups of kGroupWarps warps, one owned row at a time
 // ---------------------------------------------------------------------------
-// Shared-memory scratch of one row group.
+// Shared-memory scratch of one row group (double-buffered by iteration parity:
+// one barrier per row then orders both the next-row broadcast and the exchange
+// of the partial sums of squares).
 struct GroupScratch {
-  uint32_t job[2];   // row claimed for iteration i lives in job[i & 1]
-  float ssq[kGroupWarps];
-  uint32_t pad[2];
+  uint32_t job[2];
+  float ssq[2][kGroupWarps];
 };
 
 __device__ __forceinline__ void group_barrier(int group) {
@@ -187,17 +210,21 @@ __device__ __forceinline__ void group_barrier(int group) {
 // all-reduce would have produced).  Rows of up to 8192 values stay in registers
 // (8 x 16 bytes per thread) between the sum and the RMSNorm scaling; wider rows
 // take two passes (the rounded sums are parked in this rank's output row and read
-// back).  NVLS == true replaces the per-rank loads by one multimem.ld_reduce per
-// chunk and the per-rank result stores by one multimem.st.  WS > 0 fixes the
-// number of ranks at compile time; WS == 0 is the generic fallback.
+// back).  With a single source per chunk (one rank, or NVLS) the loads of the
+// next row are issued before the current row is scaled and stored, if that
+// row's partials have already arrived.  NVLS == true replaces the per-rank
+// loads by one multimem.ld_reduce per chunk and the per-rank result stores by
+// one multimem.st.  WS > 0 fixes the number of ranks at compile time; WS == 0
+// is the generic fallback.
 template <bool BF16, int WS, bool NVLS>
-__device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* gs, int group, int wg, int lane,
-                                            uint64_t deadline, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* gs, uint32_t gamma_smem, int group,
+                                            int wg, int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
   constexpr int BM = 128;
   constexpr int GT = kGroupWarps * 32;  // threads per row
   constexpr int CPT = 8;                // 16-byte chunks per thread held in registers
   constexpr int NS = NVLS ? 1 : (WS == 0 ? kMaxRanks : WS);
   constexpr int BATCH = NS >= CPT ? 1 : CPT / NS;  // chunks loaded together
+  constexpr bool PREFETCH = NS == 1;               // next row's loads fit in registers
   const int ws = p.ws;
   const int nsrc = NVLS ? 1 : ws;
   const int n_chunks = p.N >> 3;
@@ -272,33 +299,30 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
     f = unpack2<BF16>(h.w); o.w = norm_pack2<BF16>(f.x, f.y, rstd, w.w);
     return o;
   };
-  // sum of squares over the whole row: warp shuffle, then the group's warps through shared memory
-  auto row_ssq = [&](float ssq) -> float {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-    if (lane == 0) gs->ssq[wg] = ssq;
-    group_barrier(group);
-    float t = 0.f;
-#pragma unroll
-    for (int w = 0; w < kGroupWarps; ++w) t += gs->ssq[w];
-    return t;
+  // where owned row lr lives: global row, 128-row block, partial rows, output row
+  auto global_row = [&](int lr) -> int {
+    if (p.own_mode == OWN_BLOCK) return p.me * rows_local + lr;
+    if (p.own_mode == OWN_INTERLEAVE) return lr * ws + p.me;
+    return lr;
   };
-
-  uint32_t claimed = 0;
-  if (leader) claimed = atomicAdd(p.job_counter, 1u);
-  for (int it = 0;; ++it) {
-    if (leader) gs->job[it & 1] = claimed;
-    group_barrier(group);
-    const int lr = static_cast<int>(gs->job[it & 1]);
-    if (lr >= rows_local) break;
-    if (leader) claimed = atomicAdd(p.job_counter, 1u);  // the next row; its latency hides behind this row
-    int g;  // global row
-    if (p.own_mode == OWN_BLOCK) g = p.me * rows_local + lr;
-    else if (p.own_mode == OWN_INTERLEAVE) g = lr * ws + p.me;
-    else g = lr;
-    const int rb = g / BM;
-
-    // wait until every rank's partials for the 128-row block rb have arrived
+  auto partials_of = [&](int lr, int g) -> const uint16_t* {
+    // NVLS: partials sit at their global row in every rank's staging buffer
+    return NVLS ? reinterpret_cast<const uint16_t*>(p.mc_stage) + static_cast<long long>(g) * p.N
+                : stage + static_cast<long long>(lr) * p.N;
+  };
+  auto load_chunk = [&](uint4 (&v)[NS], const uint16_t* src0, int c) {
+#pragma unroll
+    for (int sidx = 0; sidx < NS; ++sidx) {
+      if (sidx < nsrc) {
+        if constexpr (NVLS) v[sidx] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
+        else v[sidx] = ptx::ld_cg_v4(src0 + sidx * src_stride + c * 8);
+      }
+    }
+  };
+  int ready_rb = -1;  // last 128-row block this warp has seen complete (rows are claimed in ascending order)
+  // Bounded wait until every rank's partials for block rb have arrived (0 on timeout).
+  auto wait_block = [&](int rb) -> uint32_t {
+    if (rb == ready_rb) return 1u;
     uint32_t ok = 1;
     if (lane == 0) {
       uint32_t seen = 0;
@@ -310,31 +334,60 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     __syncwarp();  // lane 0's acquire is ordered before the other lanes' loads of the partials
+    if (ok) ready_rb = rb;
+    return ok;
+  };
+  // One look at the counter, no waiting.
+  auto block_ready_now = [&](int rb) -> bool {
+    if (rb == ready_rb) return true;
+    uint32_t ok = 0;
+    if (lane == 0) ok = static_cast<int32_t>(ptx::ld_acquire_sys(my_flag + rb) - p.flag_target) >= 0 ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    if (ok) ready_rb = rb;
+    return ok != 0;
+  };
 
+  // the first row, and the claim of the one after it
+  uint32_t claimed = 0;
+  if (leader) {
+    gs->job[0] = atomicAdd(p.job_counter, 1u);
+    claimed = atomicAdd(p.job_counter, 1u);
+  }
+  group_barrier(group);
+  int lr = static_cast<int>(gs->job[0]);
+  bool have = false;  // `pre` holds the (summed) chunks of row lr, loaded during the previous iteration
+  uint4 pre[CPT];
+
+  for (int it = 0; lr < rows_local; ++it) {
+    const int par = it & 1;
+    const int g = global_row(lr);
     const int out_row = p.bcast ? g : lr;
-    // NVLS: partials sit at their global row in every rank's staging buffer
-    const uint16_t* src0 = NVLS ? reinterpret_cast<const uint16_t*>(p.mc_stage) + static_cast<long long>(g) * p.N
-                                : stage + static_cast<long long>(lr) * p.N;
-    auto load_chunk = [&](uint4 (&v)[NS], int c) {
-#pragma unroll
-      for (int sidx = 0; sidx < NS; ++sidx) {
-        if (sidx < nsrc) {
-          if constexpr (NVLS) v[sidx] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
-          else v[sidx] = ptx::ld_cg_v4(src0 + sidx * src_stride + c * 8);
-        }
-      }
-    };
+    const uint16_t* src0 = partials_of(lr, g);
+    const uint32_t ok = have ? 1u : wait_block(g / BM);
 
-    if (one_pass) {
-      uint4 h[CPT];
-      float ssq = 0.f;
-      if (ok) {
+    // ---- sum of the partial rows (and the sum of squares) ----
+    uint4 h[CPT];
+    float ssq = 0.f;
+    uint16_t* park = reinterpret_cast<uint16_t*>(p.out[p.me]);  // wide rows only
+    if (ok && one_pass) {
+      if (PREFETCH && have) {
+#pragma unroll
+        for (int u = 0; u < CPT; ++u) {
+          const int c = u * GT + tid;
+          if (c < n_chunks) {
+            h[u] = pre[u];
+            if (p.norm) ssq += sq(h[u]);
+            else store_out(out_row, c, h[u]);
+          }
+        }
+      } else {
         // software pipeline: the loads of batch k+1 are in flight while batch k is summed
         uint4 cur[BATCH][NS], nxt[BATCH][NS];
 #pragma unroll
         for (int u = 0; u < BATCH; ++u) {
           const int c = u * GT + tid;
-          if (c < n_chunks) load_chunk(cur[u], c);
+          if (c < n_chunks) load_chunk(cur[u], src0, c);
         }
 #pragma unroll
         for (int b0 = 0; b0 < CPT; b0 += BATCH) {
@@ -342,7 +395,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
 #pragma unroll
             for (int u = 0; u < BATCH; ++u) {
               const int c = (b0 + BATCH + u) * GT + tid;
-              if (c < n_chunks) load_chunk(nxt[u], c);
+              if (c < n_chunks) load_chunk(nxt[u], src0, c);
             }
           }
 #pragma unroll
@@ -363,47 +416,78 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
           }
         }
       }
-      if (p.norm) {
-        ssq = row_ssq(ssq);
-        if (ok) {
-          const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
-#pragma unroll
-          for (int u = 0; u < CPT; ++u) {
-            const int c = u * GT + tid;
-            if (c < n_chunks) store_out(out_row, c, scale(h[u], rstd, __ldg(gamma + c)));
-          }
-        }
-      }
-    } else {
+    } else if (ok) {
       // wide rows: first pass sums and parks the rounded sums in this rank's output row
-      float ssq = 0.f;
-      uint16_t* park = reinterpret_cast<uint16_t*>(p.out[p.me]);
-      if (ok) {
-        for (int c = tid; c < n_chunks; c += GT) {
-          uint4 v[NS];
-          load_chunk(v, c);
-          const uint4 h = sum_sources(v);
-          if (p.norm) {
-            ssq += sq(h);
-            ptx::st_v4(park + layout_offset(p.out_layout, out_row, c * 8), h);
-          } else {
-            store_out(out_row, c, h);
-          }
-        }
-      }
-      if (p.norm) {
-        ssq = row_ssq(ssq);
-        if (ok) {
-          const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
-          for (int c = tid; c < n_chunks; c += GT) {  // every thread re-reads exactly the chunks it wrote
-            const uint4 h = ptx::ld_cg_v4(park + layout_offset(p.out_layout, out_row, c * 8));
-            store_out(out_row, c, scale(h, rstd, __ldg(gamma + c)));
-          }
+      for (int c = tid; c < n_chunks; c += GT) {
+        uint4 v[NS];
+        load_chunk(v, src0, c);
+        const uint4 hv = sum_sources(v);
+        if (p.norm) {
+          ssq += sq(hv);
+          ptx::st_v4(park + layout_offset(p.out_layout, out_row, c * 8), hv);
+        } else {
+          store_out(out_row, c, hv);
         }
       }
     }
-    if (!ok) continue;  // keep taking part in the group barriers; later waits fail at once
-    if (p.bcast) {
+
+    // ---- one barrier: exchange the partial sums of squares, learn the next row ----
+    if (p.norm) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+      if (lane == 0) gs->ssq[par][wg] = ssq;
+    }
+    if (leader) gs->job[par ^ 1] = claimed;
+    group_barrier(group);
+    const int next_lr = static_cast<int>(gs->job[par ^ 1]);
+    if (leader && next_lr < rows_local) claimed = atomicAdd(p.job_counter, 1u);  // its latency hides behind the stores
+    if (p.norm) {
+      ssq = 0.f;
+#pragma unroll
+      for (int w = 0; w < kGroupWarps; ++w) ssq += gs->ssq[par][w];
+    }
+
+    // ---- the next row's loads go out before this row is stored, if its partials are there ----
+    have = false;
+    if constexpr (PREFETCH) {
+      if (one_pass && next_lr < rows_local) {
+        const int g2 = global_row(next_lr);
+        if (block_ready_now(g2 / BM)) {
+          const uint16_t* src2 = partials_of(next_lr, g2);
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const int c = u * GT + tid;
+            if (c < n_chunks) {
+              uint4 v[NS];
+              load_chunk(v, src2, c);
+              pre[u] = sum_sources(v);
+            }
+          }
+          have = true;
+        }
+      }
+    }
+
+    // ---- RMSNorm scaling and delivery of this row ----
+    if (p.norm && ok) {
+      const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
+      if (one_pass) {
+#pragma unroll
+        for (int u = 0; u < CPT; ++u) {
+          const int c = u * GT + tid;
+          if (c < n_chunks) {
+            store_out(out_row, c, scale(h[u], rstd, ptx::ld_shared_v4(gamma_smem + (static_cast<uint32_t>(c) << 4))));
+          }
+        }
+      } else {
+        for (int c = tid; c < n_chunks; c += GT) {  // every thread re-reads exactly the chunks it wrote
+          const uint4 hv = ptx::ld_cg_v4(park + layout_offset(p.out_layout, out_row, c * 8));
+          const uint4 wv = __ldg(gamma + c);
+          store_out(out_row, c, scale(hv, rstd, wv));
+        }
+      }
+    }
+    if (ok && p.bcast) {
       __syncwarp();  // every lane's stores of this row part precede the releases below
       if constexpr (NVLS) {
         if (lane == 0) ptx::multimem_red_release_add(p.mc_done, 1u);
@@ -411,11 +495,12 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
       }
     }
-    if (p.phase_trace != nullptr && leader) {
+    if (ok && p.phase_trace != nullptr && leader) {
       t_last = ptx::globaltimer_ns();
       if (t_first == 0) t_first = t_last;
       ++rows_done;
     }
+    lr = next_lr;
   }
   if (p.phase_trace != nullptr && leader && rows_done != 0) {
     unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
@@ -428,18 +513,18 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
 // (not inlined: the kernel calls it from two places, the communication warps
 // and the GEMM warps that join later)
 template <bool BF16>
-__device__ __noinline__ void comm_dispatch(const FusedParams& p, GroupScratch* gs, int group, int wg, int lane,
-                                              uint64_t deadline, volatile uint32_t* abort_flag) {
+__device__ __noinline__ void comm_dispatch(const FusedParams& p, GroupScratch* gs, uint32_t gamma_smem, int group, int wg,
+                                           int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
   if (p.nvls) {
-    comm_worker<BF16, 1, true>(p, gs, group, wg, lane, deadline, abort_flag);
+    comm_worker<BF16, 1, true>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag);
     return;
   }
   switch (p.ws) {
-    case 1: comm_worker<BF16, 1, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
-    case 2: comm_worker<BF16, 2, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
-    case 4: comm_worker<BF16, 4, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
-    case 8: comm_worker<BF16, 8, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
-    default: comm_worker<BF16, 0, false>(p, gs, group, wg, lane, deadline, abort_flag); break;
+    case 1: comm_worker<BF16, 1, false>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag); break;
+    case 2: comm_worker<BF16, 2, false>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag); break;
+    case 4: comm_worker<BF16, 4, false>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag); break;
+    case 8: comm_worker<BF16, 8, false>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag); break;
+    default: comm_worker<BF16, 0, false>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag); break;
   }
 }
 
@@ -462,6 +547,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   uint8_t* smem_b = smem + STAGES * T::A_BYTES;
   uint8_t* smem_epi = smem + STAGES * T::STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + T::EPI_BYTES);
+  const uint32_t gamma_smem = ptx::smem_u32(smem_epi + T::EPI_BYTES + T::BAR_BYTES);  // [N] RMSNorm weights
   uint64_t* full_bar = bars;                   // [STAGES] TMA -> MMA
   uint64_t* empty_bar = bars + STAGES;         // [STAGES] MMA -> TMA
   uint64_t* tfull_bar = bars + 2 * STAGES;     // [2] MMA -> epilogue
@@ -498,6 +584,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
   }
+  if (p.reduce && p.norm && p.N <= kGammaSmemValues) {
+    // the RMSNorm weights, once per CTA: every row group reads them for every row
+    const uint4* gamma = reinterpret_cast<const uint4*>(p.gamma);
+    for (int c = threadIdx.x; c < (p.N >> 3); c += kThreads) {
+      ptx::st_shared_v4(gamma_smem + (static_cast<uint32_t>(c) << 4), __ldg(gamma + c));
+    }
+  }
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&p.tmA);
     ptx::prefetch_tensormap(&p.tmB);
@@ -526,6 +619,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // A row panel serves every tile of its raster group (kept in L2), a B
+      // panel is read by the group's tiles at about the same time and then
+      // not again before the next group (dropped first).
+      const uint64_t pol_a = ptx::l2_policy_evict_last();
+      const uint64_t pol_b = ptx::l2_policy_evict_first();
       for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         int m_blk, n_blk;
         tile_coords(p, t, m_blk, n_blk);
@@ -561,19 +659,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
             if (cta_rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * T::STAGE_BYTES);
 #pragma unroll
             for (int h = 0; h < T::ATOMS; ++h) {  // one box of 64 K-values per swizzle atom
-              ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                                    kb * BK + h * T::ATOM_K, a_row);
-              ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
-                                    kb * BK + h * T::ATOM_K, b_row);
+              if (p.l2_hints) {
+                ptx::tma_load_2d_pair_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                                           kb * BK + h * T::ATOM_K, a_row, pol_a);
+                ptx::tma_load_2d_pair_hint(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                                           kb * BK + h * T::ATOM_K, b_row, pol_b);
+              } else {
+                ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, a_row);
+                ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, b_row);
+              }
             }
           } else {
             ptx::mbar_arrive_expect_tx(&full_bar[stage], T::STAGE_BYTES);
 #pragma unroll
             for (int h = 0; h < T::ATOMS; ++h) {
-              ptx::tma_load_2d(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                               kb * BK + h * T::ATOM_K, a_row);
-              ptx::tma_load_2d(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
-                               kb * BK + h * T::ATOM_K, b_row);
+              if (p.l2_hints) {
+                ptx::tma_load_2d_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, a_row, pol_a);
+                ptx::tma_load_2d_hint(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, b_row, pol_b);
+              } else {
+                ptx::tma_load_2d(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
+                                 kb * BK + h * T::ATOM_K, a_row);
+                ptx::tma_load_2d(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
+                                 kb * BK + h * T::ATOM_K, b_row);
+              }
             }
           }
           if (++stage == STAGES) {
@@ -854,7 +966,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       }
     } else if (p.reduce) {
       static_assert(kCommWarps == kGroupWarps, "the communication warps form one row group");
-      comm_dispatch<BF16>(p, group_scratch, 0, cw, lane, deadline, abort_flag);
+      comm_dispatch<BF16>(p, group_scratch, gamma_smem, 0, cw, lane, deadline, abort_flag);
     }
     return;
   }
@@ -893,7 +1005,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   // ===================== reduce phase, joined by the GEMM warps =====================
   {
     const int group = 1 + warp / kGroupWarps;  // warps 0-3 -> group 1, warps 4-7 -> group 2
-    comm_dispatch<BF16>(p, group_scratch + group, group, warp % kGroupWarps, lane, deadline, abort_flag);
+    comm_dispatch<BF16>(p, group_scratch + group, gamma_smem, group, warp % kGroupWarps, lane, deadline, abort_flag);
   }
 
   // All-reduce: the kernel may only end once every owner has delivered its

@@ -2,6 +2,7 @@
 
 #include <nvtx3/nvToolsExt.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 #include <stdexcept>
@@ -160,6 +161,8 @@ void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
   p.status_mirror = status_mirror_;
   p.timeout_ns = timeout_ns_;
   p.raster_group = raster_group_;
+  p.l2_hints = l2_hints_ ? 1 : 0;
+  p.raster_taper = 0;  // set by the operations that have a reduce phase
   p.phase_trace = phase_trace_;
   p.epi_layout.ld = 0;
 }
@@ -211,6 +214,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   p.flag[0] = local;
   p.job_counter = local + kFlagJob;
   if (p.raster_group == 0) p.raster_group = 8;
+  p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
   p.stage = scratch;
   p.flag_target = static_cast<uint32_t>(g.N / tc.bn);
@@ -252,7 +256,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
     p.done[r] = done_ptr(r, set);
   }
   p.epi_layout.ld = g.N;
-  if (use_nvls_ && nvls_available()) {
+  if (allreduce_uses_nvls()) {
     p.nvls = 1;
     p.epi_base[0] = heap_.local(ws_.stage[set]);  // partials stay here, [M][N]
     p.mc_stage = heap_.mc(ws_.stage[set]);
@@ -262,6 +266,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   }
   // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
+  p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
@@ -312,7 +317,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
     p.flag[r] = flag_ptr(r, set);
   }
   p.epi_layout.ld = g.N;
-  if (use_nvls_rs_ && nvls_available()) {
+  if (reducescatter_uses_nvls()) {
     p.nvls = 1;
     p.epi_base[0] = heap_.local(ws_.stage[set]);
     p.mc_stage = heap_.mc(ws_.stage[set]);
@@ -325,6 +330,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   }
   // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
+  p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));

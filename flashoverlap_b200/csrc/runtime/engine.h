@@ -57,6 +57,11 @@ class FusedEngine {
   void set_timeout_ms(long long ms) { timeout_ns_ = static_cast<unsigned long long>(ms) * 1000000ull; }
   void set_sm_count(int n) { sm_count_ = n; }
   void set_raster_group(int g) { raster_group_ = g; }
+  // L2 eviction hints on the operand loads (A row panel kept, B streamed); off by default
+  // (they help only the largest K, measured).
+  void set_l2_hints(bool on) { l2_hints_ = on; }
+  // Shrinking last raster groups for operations with a reduce phase (default on).
+  void set_raster_taper(bool on) { raster_taper_ = on; }
   // Device buffer of kTraceWords x uint64 per CTA that every following launch
   // fills with its phase timestamps (null = off).
   void set_phase_trace(unsigned long long* buf) { phase_trace_ = buf; }
@@ -127,13 +132,20 @@ class FusedEngine {
   void detach_symmetric();
   bool nvls_available() const { return heap_.valid() && heap_.has_multicast() && world_ > 1; }
   // Which operations take the NVLink SHARP path when it is available.
-  // Default: all-reduce yes (it halves the inbound traffic), reduce-scatter no
-  // (pushing partial tiles while the GEMM runs hides the transfer, a pull
-  // after the GEMM cannot).
+  // Default: all-reduce when the group has four or more ranks, reduce-scatter
+  // never.  For an output of S bytes an all-reduce moves S(1+1/n) bytes per
+  // NVLink direction through the switch against 2S(n-1)/n with peer-to-peer
+  // stores: more with two ranks, fewer from four on.  A reduce-scatter moves
+  // S(n-1)/n with peer-to-peer pushes against S pulled through the switch.
+  // Calling set_use_nvls fixes both choices by hand.
   void set_use_nvls(bool allreduce, bool reducescatter) {
-    use_nvls_ = allreduce;
-    use_nvls_rs_ = reducescatter;
+    nvls_ar_ = allreduce ? 1 : 0;
+    nvls_rs_ = reducescatter ? 1 : 0;
   }
+  bool allreduce_uses_nvls() const {
+    return nvls_available() && (nvls_ar_ < 0 ? world_ >= 4 : nvls_ar_ != 0);
+  }
+  bool reducescatter_uses_nvls() const { return nvls_available() && nvls_rs_ > 0; }
 
   // Failure-path self test: launches the bounded counter wait on a counter that
   // nothing increments, with its own short deadline.  The wait must give up,
@@ -180,8 +192,10 @@ class FusedEngine {
   unsigned long long timeout_ns_ = 20000000000ull;
   int sm_count_ = 0;
   int raster_group_ = 0;  // 0 = choose per operation
-  bool use_nvls_ = true;
-  bool use_nvls_rs_ = false;
+  bool l2_hints_ = false;
+  bool raster_taper_ = true;
+  int nvls_ar_ = -1;  // -1 = by group size, 0 = off, 1 = on
+  int nvls_rs_ = -1;
   void carve_workspace(long long elems);
   void gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M, int first_row,
                      const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream);

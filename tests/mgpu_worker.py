@@ -27,8 +27,10 @@ def main():
     rank, world, _ = init_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
     impl = make_overlap_impl(timeout_ms=4000, max_m=4096, max_n=4096)
+    if impl.nvls_available():
+        impl.set_use_nvls(True, False)  # exercise the multimem path at every group size
     if rank == 0:
-        print(f"mode: {'NVLS multimem' if impl.nvls_available() else 'P2P stores'}", flush=True)
+        print(f"mode: {'NVLS multimem' if impl.allreduce_uses_nvls() else 'P2P stores'}", flush=True)
     failures = 0
 
     def check(name, got, want, tol):
