@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--algo", type=int, default=3, help="tile configuration (3 = 256x256 CTA pair)")
+    ap.add_argument("--algo", type=int, default=8, help="tile configuration (8 = 256x256x128 CTA pair)")
     ap.add_argument("--no-detail", action="store_true", help="skip the baseline, the checks and the other shapes")
     return ap.parse_args()
 

@@ -216,6 +216,10 @@ __device__ __forceinline__ void group_barrier(int group) {
 // loads by one multimem.ld_reduce per chunk and the per-rank result stores by
 // one multimem.st.  WS > 0 fixes the number of ranks at compile time; WS == 0
 // is the generic fallback.
+// (Inlined into the kernel, which calls it from a single place: the parameter
+// block must stay a kernel parameter read through the constant bank.  Behind a
+// function call it would be read through a generic pointer, one global load per
+// field access, which made every row several times slower.)
 template <bool BF16, int WS, bool NVLS>
 __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* gs, uint32_t gamma_smem, int group,
                                             int wg, int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
@@ -257,8 +261,8 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
     }
   };
   auto sum_sources = [&](const uint4 (&v)[NS]) -> uint4 {
-    if constexpr (NVLS) {
-      return v[0];  // summed by the switch in fp32, rounded once
+    if constexpr (NVLS || WS == 1) {
+      return v[0];  // NVLS: summed by the switch in fp32, rounded once; one rank: nothing to add
     } else {
       float a[8];
 #pragma unroll
@@ -356,15 +360,27 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   }
   group_barrier(group);
   int lr = static_cast<int>(gs->job[0]);
+  constexpr uint32_t kDeliveryBatch = 4;
+  uint32_t undelivered = 0;  // rows this warp has stored but not yet counted on the delivery counters
   bool have = false;  // `pre` holds the (summed) chunks of row lr, loaded during the previous iteration
   uint4 pre[CPT];
 
+#ifdef FO_ROW_STAMPS
+  unsigned long long* dbg = (p.phase_trace != nullptr && blockIdx.x == 5 && leader)
+                                ? p.phase_trace + static_cast<unsigned long long>(kTraceWords) * gridDim.x + group * 128
+                                : nullptr;
+#define FO_STAMP(k) if (dbg != nullptr && it < 16) dbg[it * 8 + (k)] = ptx::globaltimer_ns();
+#else
+#define FO_STAMP(k)
+#endif
   for (int it = 0; lr < rows_local; ++it) {
     const int par = it & 1;
+    FO_STAMP(0)
     const int g = global_row(lr);
     const int out_row = p.bcast ? g : lr;
     const uint16_t* src0 = partials_of(lr, g);
     const uint32_t ok = have ? 1u : wait_block(g / BM);
+    FO_STAMP(1)
 
     // ---- sum of the partial rows (and the sum of squares) ----
     uint4 h[CPT];
@@ -431,6 +447,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       }
     }
 
+    FO_STAMP(2)
     // ---- one barrier: exchange the partial sums of squares, learn the next row ----
     if (p.norm) {
 #pragma unroll
@@ -447,6 +464,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       for (int w = 0; w < kGroupWarps; ++w) ssq += gs->ssq[par][w];
     }
 
+    FO_STAMP(3)
     // ---- the next row's loads go out before this row is stored, if its partials are there ----
     have = false;
     if constexpr (PREFETCH) {
@@ -468,6 +486,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       }
     }
 
+    FO_STAMP(4)
     // ---- RMSNorm scaling and delivery of this row ----
     if (p.norm && ok) {
       const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
@@ -487,13 +506,19 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         }
       }
     }
-    if (ok && p.bcast) {
-      __syncwarp();  // every lane's stores of this row part precede the releases below
+    FO_STAMP(5)
+    // Delivery counts are only read at the end of the kernel, and a release
+    // at system scope waits for this warp's stores to be acknowledged by the
+    // peers: signal a batch of rows at a time.
+    if (ok && p.bcast) ++undelivered;
+    if (undelivered != 0 && (undelivered == kDeliveryBatch || next_lr >= rows_local)) {
+      __syncwarp();  // every lane's stores of these row parts precede the releases below
       if constexpr (NVLS) {
-        if (lane == 0) ptx::multimem_red_release_add(p.mc_done, 1u);
+        if (lane == 0) ptx::multimem_red_release_add(p.mc_done, undelivered);
       } else {
-        if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], 1u);
+        if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], undelivered);
       }
+      undelivered = 0;
     }
     if (ok && p.phase_trace != nullptr && leader) {
       t_last = ptx::globaltimer_ns();
@@ -510,10 +535,8 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   }
 }
 
-// (not inlined: the kernel calls it from two places, the communication warps
-// and the GEMM warps that join later)
 template <bool BF16>
-__device__ __noinline__ void comm_dispatch(const FusedParams& p, GroupScratch* gs, uint32_t gamma_smem, int group, int wg,
+__device__ __forceinline__ void comm_dispatch(const FusedParams& p, GroupScratch* gs, uint32_t gamma_smem, int group, int wg,
                                            int lane, uint64_t deadline, volatile uint32_t* abort_flag) {
   if (p.nvls) {
     comm_worker<BF16, 1, true>(p, gs, gamma_smem, group, wg, lane, deadline, abort_flag);
@@ -929,6 +952,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
     }
   }
 
+  int group = 0;  // row group of this warp in the reduce phase
+  int wg = 0;     // warp inside the group
   if (warp >= kGemmWarps) {
     // ===================== communication warps =====================
     const int cw = warp - kGemmWarps;
@@ -964,49 +989,50 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           ptx::red_relaxed_sys_add(p.ag_flag[d], 1u);
         }
       }
-    } else if (p.reduce) {
-      static_assert(kCommWarps == kGroupWarps, "the communication warps form one row group");
-      comm_dispatch<BF16>(p, group_scratch, gamma_smem, 0, cw, lane, deadline, abort_flag);
+      return;
     }
-    return;
-  }
-
-  // ===================== teardown of the GEMM phase (GEMM warps only) =====================
-  __syncwarp();
-  ptx::tc_fence_before_sync();
-  ptx::named_barrier_sync(8, kGemmThreads);
-  if constexpr (CTAS == 2) {
-    // The partner may still read this CTA's operands or signal its barriers:
-    // each CTA tells the other that its GEMM warps are done and waits (bounded)
-    // to hear the same.
-    if (threadIdx.x == 0) {
-      ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(pair_bar), cta_rank ^ 1u));
-      if (!ptx::mbar_wait_cluster(pair_bar, 0u, deadline)) {
-        report_error(p, ST_TIMEOUT_PIPE, 0x700u, 0, 0);
-        *abort_flag = 1;
-      }
-    }
+    if (!p.reduce) return;
+    static_assert(kCommWarps == kGroupWarps, "the communication warps form one row group");
+    group = 0;  // reduces rows from the first cycle on
+    wg = cw;
+  } else {
+    // ===================== teardown of the GEMM phase (GEMM warps only) =====================
+    __syncwarp();
+    ptx::tc_fence_before_sync();
     ptx::named_barrier_sync(8, kGemmThreads);
+    if constexpr (CTAS == 2) {
+      // The partner may still read this CTA's operands or signal its barriers:
+      // each CTA tells the other that its GEMM warps are done and waits (bounded)
+      // to hear the same.
+      if (threadIdx.x == 0) {
+        ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(pair_bar), cta_rank ^ 1u));
+        if (!ptx::mbar_wait_cluster(pair_bar, 0u, deadline)) {
+          report_error(p, ST_TIMEOUT_PIPE, 0x700u, 0, 0);
+          *abort_flag = 1;
+        }
+      }
+      ptx::named_barrier_sync(8, kGemmThreads);
+    }
+    if (warp == 2) {
+      ptx::tc_fence_after_sync();
+      if constexpr (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, T::TMEM_COLS);
+      else ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
+    }
+    if (p.phase_trace != nullptr && threadIdx.x == 0) {
+      unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
+      tr[1] = ptx::globaltimer_ns();
+      int mine = 0;
+      for (int t = first_tile; t < num_tiles; t += tile_stride) ++mine;
+      tr[3] = static_cast<unsigned long long>(mine);
+    }
+    if (!p.reduce || *abort_flag) return;
+    // out of tiles: the GEMM warps join the reduce phase as two more row groups
+    group = 1 + warp / kGroupWarps;  // warps 0-3 -> group 1, warps 4-7 -> group 2
+    wg = warp % kGroupWarps;
   }
-  if (warp == 2) {
-    ptx::tc_fence_after_sync();
-    if constexpr (CTAS == 2) ptx::tmem_dealloc_pair(tmem_base, T::TMEM_COLS);
-    else ptx::tmem_dealloc(tmem_base, T::TMEM_COLS);
-  }
-  if (p.phase_trace != nullptr && threadIdx.x == 0) {
-    unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
-    tr[1] = ptx::globaltimer_ns();
-    int mine = 0;
-    for (int t = first_tile; t < num_tiles; t += tile_stride) ++mine;
-    tr[3] = static_cast<unsigned long long>(mine);
-  }
-  if (!p.reduce || *abort_flag) return;
 
-  // ===================== reduce phase, joined by the GEMM warps =====================
-  {
-    const int group = 1 + warp / kGroupWarps;  // warps 0-3 -> group 1, warps 4-7 -> group 2
-    comm_dispatch<BF16>(p, group_scratch + group, gamma_smem, group, warp % kGroupWarps, lane, deadline, abort_flag);
-  }
+  // ===================== reduce phase (every warp ends up here) =====================
+  comm_dispatch<BF16>(p, group_scratch + group, gamma_smem, group, wg, lane, deadline, abort_flag);
 
   // All-reduce: the kernel may only end once every owner has delivered its
   // rows into this rank's output.

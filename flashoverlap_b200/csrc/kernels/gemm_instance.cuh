@@ -10,9 +10,8 @@
 
 namespace fo {
 
-// Launches one CTA per requested SM (a cluster of two for CTA pairs).  The
-// launch is cooperative: CTAs wait on counters that other CTAs of the same
-// grid bump, so either the whole grid is resident at once or the launch fails.
+// Launches one CTA per requested SM (a cluster of two for CTA pairs), as a
+// cooperative launch when cooperative_launch_enabled().
 // Raises the kernel's dynamic shared-memory limit on the current device (once
 // per device and instance; a device index beyond the cache is set every time).
 template <int BN, int BK, bool BF16, int CTAS>

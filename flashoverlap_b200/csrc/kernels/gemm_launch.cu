@@ -24,7 +24,7 @@ TileConfig algo_config(int algo) { return kAlgoTable[(algo < 0 || algo >= kNumAl
 bool cooperative_launch_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("FLASHOVERLAP_COOPERATIVE");
-    return !(e != nullptr && (std::strcmp(e, "0") == 0 || std::strcmp(e, "off") == 0));
+    return e != nullptr && (std::strcmp(e, "1") == 0 || std::strcmp(e, "on") == 0);
   }();
   return on;
 }

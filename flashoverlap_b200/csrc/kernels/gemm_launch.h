@@ -47,9 +47,13 @@ int device_sm_count();
 // a device with a higher index is handled uncached.
 constexpr int kMaxDevices = 64;
 
-// Fused launches are cooperative by default (the driver guarantees that all
-// CTAs are resident together, or refuses).  FLASHOVERLAP_COOPERATIVE=0 in the
-// environment turns the attribute off.
+// FLASHOVERLAP_COOPERATIVE=1 in the environment makes fused launches
+// cooperative: the driver then guarantees that all CTAs are resident together
+// (or refuses the launch), which matters when something else may hold SMs.
+// Off by default: a profiler that replays kernels refused the cooperative
+// launch (LaunchFailed under `ncu --set full`).  Without it, fused launches on
+// one GPU must not overlap one another; a CTA that cannot become resident
+// makes the waits of the resident ones run into their deadline.
 bool cooperative_launch_enabled();
 
 }  // namespace fo

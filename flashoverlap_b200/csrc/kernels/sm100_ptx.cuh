@@ -435,8 +435,12 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
   asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+// Streaming 16-byte store: the data is never read again through this SM's L1,
+// and with nearly all of the SM's memory given to shared memory the little L1
+// that is left must stay available to the stack (register spills).
 __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
-  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
                : "memory");
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t saddr, const uint4& v) {

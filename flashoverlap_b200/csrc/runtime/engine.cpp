@@ -273,7 +273,8 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   p.norm = norm.gamma != nullptr;
   p.gamma = norm.gamma;
   p.eps = norm.eps;
-  p.bcast = 1;
+  // with one rank there is nobody to deliver to: rows go to the result buffer like a reduce-scatter's
+  p.bcast = world_ > 1 ? 1 : 0;
   if (out_layout != nullptr) p.out_layout = *out_layout;
   else p.out_layout.ld = g.N;
   p.done_target = static_cast<uint32_t>(g.M) * kGroupWarps;  // one delivery count per warp and row

@@ -14,11 +14,15 @@ from flashoverlap_b200.utils import config as cfg
 pytestmark = pytest.mark.gpu
 
 
+def tiles_of(data, M, N):
+    return (M // data["BM"]) * (N // data["BN"])
+
+
 def test_profile_hint_search_and_use(tmp_path):
     M, N, K = 1024, 2048, 256
     impl = make_overlap_impl(timeout_ms=3000)
     BM, BN, dur, algo = profile_gemm(impl, M, N, K, torch.float16, warmup=2, reps=5)
-    assert len(algo) == 5 and dur == sorted(dur) and all(d > 0 for d in dur)
+    assert len(algo) == min(10, len(cfg.ALGO_TILES)) and dur == sorted(dur) and all(d > 0 for d in dur)
     cfg.save_stage1(M, N, K, BM, BN, dur, algo, tmp_path)
 
     tiles = (M // BM[0]) * (N // BN[0])
@@ -33,6 +37,13 @@ def test_profile_hint_search_and_use(tmp_path):
     data = cfg.load_config(M, N, K, tmp_path)
     cfg.validate_stage2(data, M, N)
     assert data["Algo"] == sol["Algo"] and data["search"] == "predictive" and data["fused_dur"] > 0
+    assert sum(data["cSeg"]) == tiles_of(data, M, N) and data["two_stream_dur"] > 0 and data["candidates_timed"] >= 1
+
+    # exhaustive search on the same stage-1 lists: every candidate is timed, the file is rewritten
+    ex = search.exhaustive_search(impl, M, N, K, "all_reduce", path=tmp_path, reps=3, verbose=False, seg_reps=3)
+    data = cfg.load_config(M, N, K, tmp_path)
+    cfg.validate_stage2(data, M, N)
+    assert data["search"] == "exhaustive" and data["Algo"] == ex["Algo"]
 
     # the tuned file drives the reference-compatible layer + reorder-aware RMSNorm
     layer = OverlapRowParallelLayer(0, 1, K, N, M, data, "all_reduce", [0] * 16)

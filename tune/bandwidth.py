@@ -21,7 +21,8 @@ from flashoverlap_b200.utils import config as cfg  # noqa: E402
 
 def build_parser():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--comm_op", default="all_reduce", choices=list(COMM_OPS))
+    ap.add_argument("--comm_op", default=["all_reduce"], choices=list(COMM_OPS), nargs="+",
+                    help="one or more curves to measure in this run")
     ap.add_argument("--dtype", default="float16", choices=sorted(DTYPES))
     ap.add_argument("--points", type=int, default=36)
     ap.add_argument("--max_elements", type=int, default=None)
@@ -36,33 +37,39 @@ def build_parser():
 
 
 def run(args, rank, world, gather_ranks=False):
+    """Measures every curve named in args.comm_op with one implementation object;
+    returns {comm_op: (curve, per-rank times or None)}."""
     multinode = args.multinode or int(os.environ.get("GROUP_WORLD_SIZE", "1")) > 1
-    own = args.comm_op not in NCCL_OPS
-    max_el = args.max_elements
-    if own and max_el is None:
-        max_el = 64 << 20  # the symmetric workspace holds 128 MiB per buffer
-    need = (max_el or 2 ** 29) if own else 8192 * 8192
-    impl = make_overlap_impl(nvls=True if args.comm_op.startswith("multimem") else None, max_m=8192,
-                             max_n=max(8192, need // 8192))
-    if args.comm_op.startswith("multimem") and not impl.nvls_available():
+    ops = list(args.comm_op) if isinstance(args.comm_op, (list, tuple)) else [args.comm_op]
+    any_own = any(op not in NCCL_OPS for op in ops)
+    any_mm = any(op.startswith("multimem") for op in ops)
+    max_own = args.max_elements if args.max_elements is not None else 64 << 20  # the workspace holds 128 MiB per buffer
+    impl = make_overlap_impl(nvls=True if any_mm else None, max_m=8192, max_n=max(8192, max_own // 8192 if any_own else 0))
+    out = {}
+    tables = []
+    for op in ops:
+        if op.startswith("multimem") and not impl.nvls_available():
+            if rank == 0:
+                print(f"{op}: no multicast mapping on this machine, cannot be measured")
+            continue
+        max_el = args.max_elements if op in NCCL_OPS else max_own
+        res = measure_curve(impl, op, DTYPES[args.dtype], args.points, args.warmup, args.reps, max_el,
+                            args.chunk_bytes, args.ctas, gather_ranks=gather_ranks)
+        curve, per_rank = (res if gather_ranks else (res, None))
+        impl.check_status()
+        out[op] = (curve, per_rank)
         if rank == 0:
-            print("no multicast mapping on this machine: the multimem curves cannot be measured")
-        return None, None
-    res = measure_curve(impl, args.comm_op, DTYPES[args.dtype], args.points, args.warmup, args.reps, max_el,
-                        args.chunk_bytes, args.ctas, gather_ranks=gather_ranks)
-    curve, per_rank = (res if gather_ranks else (res, None))
-    impl.check_status()
-    if rank == 0:
-        f = cfg.save_bandwidth(curve, args.comm_op, world, multinode, args.path)
-        png = str(f)[:-3] + ".png"
-        plotted = plot_curve(curve, f"{args.comm_op} x{world}", png)
-        text = curve_table(curve, args.comm_op, world)
-        print(text, end="")
-        if args.table:
-            with open(args.table, "w") as fh:
-                fh.write(text)
-        print(f"saved {f}" + (f" and {png}" if plotted else ""))
-    return curve, per_rank
+            f = cfg.save_bandwidth(curve, op, world, multinode, args.path)
+            png = str(f)[:-3] + ".png"
+            plotted = plot_curve(curve, f"{op} x{world}", png)
+            text = curve_table(curve, op, world)
+            tables.append(text)
+            print(text, end="")
+            print(f"saved {f}" + (f" and {png}" if plotted else ""))
+    if rank == 0 and args.table and tables:
+        with open(args.table, "w") as fh:
+            fh.write("\n".join(tables))
+    return out
 
 
 def main():

@@ -30,17 +30,19 @@ def main():
     args.multinode = True
     rank, world = start(retries=args.rendezvous_retries)
     nodes = int(os.environ.get("GROUP_WORLD_SIZE", os.environ.get("NNODES", "1")))
-    if args.comm_op not in NCCL_OPS and nodes > 1:
+    own = [op for op in args.comm_op if op not in NCCL_OPS]
+    if own and nodes > 1:
         if rank == 0:
-            print(f"{args.comm_op} needs peer-mapped memory: measure it inside one node with tune/bandwidth.py")
+            print(f"{own} need peer-mapped memory: measure them inside one node with tune/bandwidth.py")
         finish()
         return 2
-    curve, per_rank = bandwidth.run(args, rank, world, gather_ranks=True)
-    if rank == 0 and per_rank is not None and per_rank.numel() > 0:
-        print("# per-size times over the ranks (ms): min mean max slowest-rank")
-        for (n, _), row in zip(curve.tolist(), per_rank.tolist()):
-            worst = max(range(len(row)), key=lambda i: row[i])
-            print(f"{int(n):>12d} {min(row):9.4f} {sum(row) / len(row):9.4f} {max(row):9.4f} {worst:4d}")
+    results = bandwidth.run(args, rank, world, gather_ranks=True)
+    for op, (curve, per_rank) in results.items():
+        if rank == 0 and per_rank is not None and per_rank.numel() > 0:
+            print(f"# {op}: per-size times over the ranks (ms): min mean max slowest-rank")
+            for (n, _), row in zip(curve.tolist(), per_rank.tolist()):
+                worst = max(range(len(row)), key=lambda i: row[i])
+                print(f"{int(n):>12d} {min(row):9.4f} {sum(row) / len(row):9.4f} {max(row):9.4f} {worst:4d}")
     finish()
     return 0
 
