@@ -135,6 +135,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("attach_symmetric", &OverlapImpl::AttachSymmetric)
       .def("detach_symmetric", &OverlapImpl::DetachSymmetric)
       .def("set_use_nvls", &OverlapImpl::SetUseNvls)
+      .def("set_allgather_multicast", &OverlapImpl::SetAllGatherMulticast)
       .def("nvls_available", &OverlapImpl::NvlsAvailable)
       .def("allreduce_uses_nvls", &OverlapImpl::AllReduceUsesNvls)
       .def("p2p_push", &OverlapImpl::P2pPush)

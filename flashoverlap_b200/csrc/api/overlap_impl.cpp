@@ -625,6 +625,7 @@ void OverlapImpl::DetachSymmetric() {
   engine_.detach_symmetric();
 }
 void OverlapImpl::SetUseNvls(bool allreduce, bool reducescatter) { engine_.set_use_nvls(allreduce, reducescatter); }
+void OverlapImpl::SetAllGatherMulticast(bool on) { engine_.set_allgather_multicast(on); }
 bool OverlapImpl::NvlsAvailable() { return engine_.nvls_available(); }
 bool OverlapImpl::AllReduceUsesNvls() { return engine_.allreduce_uses_nvls(); }
 

@@ -87,6 +87,9 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Collective.  Drops the attached memory again (used when some rank could not map it).
   void DetachSymmetric();
   void SetUseNvls(bool allreduce, bool reducescatter);
+  // All-gather -> GEMM pushes the shard through the switch (one multimem.st per
+  // chunk) when a multicast mapping exists; false = peer-to-peer stores.
+  void SetAllGatherMulticast(bool on);
   bool NvlsAvailable();
   // Whether the fused all-reduce currently takes the NVLink SHARP path.
   bool AllReduceUsesNvls();

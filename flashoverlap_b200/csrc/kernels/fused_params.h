@@ -130,6 +130,11 @@ struct alignas(64) FusedParams {
   long long ag_bytes[kMaxRanks];        // their size in bytes (multiple of 16, may be 0)
   void* ag_dst[kMaxRanks];       // where this rank's shard lives in rank r's gathered A
   uint32_t* ag_flag[kMaxRanks];  // rank r's a_ready counter for this rank
+  // All-gather over NVLink SHARP (every rank receives the same rows): multicast
+  // address of this rank's slot in the gathered A and of its a_ready counter;
+  // one multimem.st per chunk then replaces the stores to every peer.  Null = peer-to-peer stores.
+  void* ag_mc_dst;
+  uint32_t* ag_mc_flag;
 
   // ---- reduce phase ---------------------------------------------------------
   int reduce;                      // 0 = kernel ends after the GEMM

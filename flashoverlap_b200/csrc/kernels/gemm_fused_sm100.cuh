@@ -966,6 +966,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       // fences at system scope and bumps that rank's shard counter.
       const long long stride = static_cast<long long>(gridDim.x) * (kCommWarps * 32);
       const long long first = static_cast<long long>(blockIdx.x) * (kCommWarps * 32) + cw * 32 + lane;
+      if (p.ag_mc_dst != nullptr) {
+        // all-gather through the switch: one multicast store per chunk lands on every rank
+        const long long chunks = p.ag_bytes[p.me] >> 4;
+        const char* src = static_cast<const char*>(p.ag_src[p.me]);
+        char* dst = static_cast<char*>(p.ag_mc_dst);
+        long long c = first;
+        for (; c + 7 * stride < chunks; c += 8 * stride) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(src + ((c + u * stride) << 4));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) ptx::multimem_st_v4(dst + ((c + u * stride) << 4), v[u]);
+        }
+        for (; c < chunks; c += stride) {
+          ptx::multimem_st_v4(dst + (c << 4), *reinterpret_cast<const uint4*>(src + (c << 4)));
+        }
+        __syncwarp();
+        if (lane == 0) {
+          ptx::fence_acq_rel_sys();
+          ptx::multimem_red_relaxed_add(p.ag_mc_flag, 1u);
+        }
+        return;
+      }
       for (int j = 0; j < p.ws; ++j) {
         int d = p.me - j;
         if (d < 0) d += p.ws;

@@ -355,7 +355,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
 // first_row: where this rank's own block starts (the GEMM begins there).
 void FusedEngine::gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M,
                                 int first_row, const void* B, void* C, int N, int K, DType dtype, int algo,
-                                const char* op, cudaStream_t stream) {
+                                const char* op, cudaStream_t stream, size_t mc_slot_offset) {
   NvtxRange range(op);
   const TileConfig tc = algo_config(algo);
   const int set = static_cast<int>(calls_ & 1ull);
@@ -396,6 +396,11 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
   p.force_full_grid = 1;
   // ag_dst is filled by the callers' layout: where my block lives on rank r
   for (int r = 0; r < world_; ++r) p.ag_dst[r] = ag_dst_scratch_[r];
+  if (mc_slot_offset != kNoMulticast && nvls_available() && nvls_ag_) {
+    // every rank receives the same rows: push them once through the switch
+    p.ag_mc_dst = static_cast<char*>(heap_.mc(ws_.stage[set])) + mc_slot_offset;
+    p.ag_mc_flag = static_cast<uint32_t*>(heap_.mc(ws_.flags[set])) + kFlagAReady + rank_;
+  }
   const char* why = nullptr;
   check_launch(launch_fused(g, p, stream, &why), why, op);
   ++calls_;
@@ -421,7 +426,8 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
     src_end[r] = (r + 1) * rows;
     ag_dst_scratch_[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + shard_bytes * rank_;
   }
-  gathered_gemm(src_for, bytes_for, src_end, M, rank_ * rows, B, C, N, K, dtype, algo, "allgather_gemm", stream);
+  gathered_gemm(src_for, bytes_for, src_end, M, rank_ * rows, B, C, N, K, dtype, algo, "allgather_gemm", stream,
+                shard_bytes * rank_);
 }
 
 int FusedEngine::a2a_padded_rows(const int* mlen, int algo) const {
@@ -470,7 +476,8 @@ void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int
   }
   // Rows between `acc` and the padded height belong to nobody: the GEMM reads
   // whatever an earlier call left there and writes scratch rows of C.
-  gathered_gemm(src_for, bytes_for, src_end, m_pad, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream);
+  gathered_gemm(src_for, bytes_for, src_end, m_pad, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream,
+                kNoMulticast);  // every destination gets different rows
 }
 
 void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {

@@ -142,6 +142,8 @@ class FusedEngine {
     nvls_ar_ = allreduce ? 1 : 0;
     nvls_rs_ = reducescatter ? 1 : 0;
   }
+  // All-gather -> GEMM: push the shard with one multicast store per chunk (default when possible).
+  void set_allgather_multicast(bool on) { nvls_ag_ = on; }
   bool allreduce_uses_nvls() const {
     return nvls_available() && (nvls_ar_ < 0 ? world_ >= 4 : nvls_ar_ != 0);
   }
@@ -197,8 +199,11 @@ class FusedEngine {
   int nvls_ar_ = -1;  // -1 = by group size, 0 = off, 1 = on
   int nvls_rs_ = -1;
   void carve_workspace(long long elems);
+  static constexpr size_t kNoMulticast = ~size_t(0);
   void gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M, int first_row,
-                     const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream);
+                     const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream,
+                     size_t mc_slot_offset);
+  bool nvls_ag_ = true;  // all-gather pushes go through the switch when a multicast mapping exists
   unsigned long long* phase_trace_ = nullptr;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
   void* ag_dst_scratch_[kMaxRanks] = {};  // destination of this rank's block on every rank (per call)

@@ -1,10 +1,10 @@
 """One small case of one kernel, a few launches, for a profiler run:
 
-    python test/profile_case.py gemm 4096 8192 8192 --algo 3
-    python test/profile_case.py gemm_rmsnorm 4096 8192 1024 --algo 3 --dtype float16
-    python test/profile_case.py rmsnorm 4096 8192
+    python tool/profile_case.py gemm 4096 8192 8192 --algo 3
+    python tool/profile_case.py gemm_rmsnorm 4096 8192 1024 --algo 3 --dtype float16
+    python tool/profile_case.py rmsnorm 4096 8192
 
-    ncu --set full --clock-control none -k regex:gemm_fused -s 2 -c 1 -o out python test/profile_case.py gemm ...
+    ncu --set full --clock-control none -k regex:gemm_fused -s 2 -c 1 -o out python tool/profile_case.py gemm ...
 
 (Single GPU only: a profiler replays every kernel many times, which a kernel
 that waits for other ranks does not survive.)
