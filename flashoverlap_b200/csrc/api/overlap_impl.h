@@ -87,8 +87,8 @@ class OverlapImpl : public torch::CustomClassHolder {
   // Collective.  Drops the attached memory again (used when some rank could not map it).
   void DetachSymmetric();
   void SetUseNvls(bool allreduce, bool reducescatter);
-  // All-gather -> GEMM pushes the shard through the switch (one multimem.st per
-  // chunk) when a multicast mapping exists; false = peer-to-peer stores.
+  // All-gather -> GEMM: true pushes the shard through the switch (one multimem.st
+  // per chunk, needs a multicast mapping); false (default) = ring of peer-to-peer stores.
   void SetAllGatherMulticast(bool on);
   bool NvlsAvailable();
   // Whether the fused all-reduce currently takes the NVLink SHARP path.

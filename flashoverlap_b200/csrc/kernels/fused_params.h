@@ -98,7 +98,8 @@ struct alignas(64) FusedParams {
   int raster_group;  // tile rows walked column-major together (L2 reuse of B)
   int raster_taper;  // 1 = the last groups shrink by halves so that little is left to communicate after the last tile
   int force_full_grid;  // launch the requested number of CTAs even when there are fewer tiles
-  int rot;           // first tile row (rotates ranks apart in block-ownership mode)
+  int rot;           // first tile row of the walk (gathered operands start at the rank's own rows)
+  int owner_stride;  // > 0 (block ownership): tile rows per owner; the walk then cycles through the owners
   int l2_hints;      // 1 = TMA loads carry L2 eviction hints (A panel kept, B panel streamed)
 
   // ---- GEMM epilogue destination -------------------------------------------

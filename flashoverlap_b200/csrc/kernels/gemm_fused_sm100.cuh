@@ -178,8 +178,18 @@ __device__ __forceinline__ void tile_coords(const FusedParams& p, int t, int& m_
     }
     rows_here = size;
   }
-  const int mb = first + r % rows_here;
+  int mb = first + r % rows_here;
   n_blk = r / rows_here;
+  if (p.owner_stride > 0) {
+    // Contiguous row ownership: position mb of the walk is tile row
+    // (mb % ws) of ... every owner in turn, so that any stretch of the walk
+    // sends to all owners alike and every owner's rows complete progressively
+    // (walking owner by owner would complete an owner's rows only when the
+    // LAST rank reaches its block, i.e. at the very end).  Each rank starts the
+    // cycle at a different owner.
+    const int o = (mb + p.me) % p.ws;
+    mb = o * p.owner_stride + mb / p.ws;
+  }
   m_blk = mb + p.rot;
   if (m_blk >= p.TM) m_blk -= p.TM;
 }

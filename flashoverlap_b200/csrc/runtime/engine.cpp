@@ -301,8 +301,9 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   if (g.M % world_ != 0) throw std::runtime_error("gemm_reducescatter: M must be divisible by the world size");
   if (g.M / 128 > kMaxTileRows) throw std::runtime_error("gemm_reducescatter: too many tile rows");
   const int rows_local = g.M / world_;
-  if (!interleave && world_ > 1 && rows_local % 128 != 0) {
-    throw std::runtime_error("gemm_reducescatter: contiguous ownership needs (M / world) % 128 == 0");
+  if (!interleave && world_ > 1 && rows_local % tc.bm != 0) {
+    throw std::runtime_error("gemm_reducescatter: contiguous ownership needs (M / world) to be a multiple of the tile "
+                             "height (" + std::to_string(tc.bm) + " for this Algo)");
   }
   ensure_workspace(g.M, g.N);
   const int set = static_cast<int>(calls_ & 1ull);
@@ -325,9 +326,9 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
     p.mc_flag = static_cast<uint32_t*>(heap_.mc(ws_.flags[set]));
   }
   if (p.own_mode == OWN_BLOCK) {
-    // start with the tile rows of the next rank so that at any moment the
-    // ranks push to different owners
-    p.rot = ((rank_ + 1) % world_) * (rows_local / tc.bm);
+    // the walk cycles through the owners (a different first owner on every rank): all links are busy at
+    // any moment and every owner's rows complete progressively instead of all at the end
+    p.owner_stride = rows_local / tc.bm;
   }
   // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
@@ -474,9 +475,15 @@ void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int
     acc += mlen[i * world_ + rank_];
     src_end[i] = acc;
   }
-  // Rows between `acc` and the padded height belong to nobody: the GEMM reads
-  // whatever an earlier call left there and writes scratch rows of C.
-  gathered_gemm(src_for, bytes_for, src_end, m_pad, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream,
+  // This rank multiplies the rows it received, rounded up to whole tiles (rows
+  // between `acc` and that height belong to nobody: the GEMM reads whatever an
+  // earlier call left there and writes scratch rows of C).  Ranks that received
+  // fewer rows launch a smaller GEMM; the workspace is sized for the largest.
+  const TileConfig tc_own = algo_config(algo);
+  int m_own = (acc + tc_own.bm - 1) / tc_own.bm * tc_own.bm;
+  if (m_own < tc_own.bm) m_own = tc_own.bm;
+  if (m_own > m_pad) m_own = m_pad;
+  gathered_gemm(src_for, bytes_for, src_end, m_own, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream,
                 kNoMulticast);  // every destination gets different rows
 }
 

@@ -142,11 +142,13 @@ class FusedEngine {
     nvls_ar_ = allreduce ? 1 : 0;
     nvls_rs_ = reducescatter ? 1 : 0;
   }
-  // All-gather -> GEMM: push the shard with one multicast store per chunk (default when possible).
+  // All-gather -> GEMM: push the shard with one multicast store per chunk (off by default, see nvls_ag_).
   void set_allgather_multicast(bool on) { nvls_ag_ = on; }
   bool allreduce_uses_nvls() const {
-    return nvls_available() && (nvls_ar_ < 0 ? world_ >= 4 : nvls_ar_ != 0);
+    return nvls_available() && (nvls_ar_ < 0 ? nvls_auto_min_world_ > 0 && world_ >= nvls_auto_min_world_ : nvls_ar_ != 0);
   }
+  // Smallest group for which the all-reduce takes NVLink SHARP by itself (0 = never).
+  void set_nvls_auto_min_world(int n) { nvls_auto_min_world_ = n; }
   bool reducescatter_uses_nvls() const { return nvls_available() && nvls_rs_ > 0; }
 
   // Failure-path self test: launches the bounded counter wait on a counter that
@@ -197,13 +199,17 @@ class FusedEngine {
   bool l2_hints_ = false;
   bool raster_taper_ = true;
   int nvls_ar_ = -1;  // -1 = by group size, 0 = off, 1 = on
+  int nvls_auto_min_world_ = 4;
   int nvls_rs_ = -1;
   void carve_workspace(long long elems);
   static constexpr size_t kNoMulticast = ~size_t(0);
   void gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M, int first_row,
                      const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream,
                      size_t mc_slot_offset);
-  bool nvls_ag_ = true;  // all-gather pushes go through the switch when a multicast mapping exists
+  // All-gather pushes through the switch (one multimem.st per chunk) deliver every shard at the same time,
+  // at the end; the ring of peer-to-peer stores delivers one shard per step in the order the GEMM consumes
+  // them, which is what lets the GEMM overlap the transfer: multicast is an option, not the default.
+  bool nvls_ag_ = false;
   unsigned long long* phase_trace_ = nullptr;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
   void* ag_dst_scratch_[kMaxRanks] = {};  // destination of this rank's block on every rank (per call)

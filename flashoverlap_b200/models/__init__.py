@@ -2,6 +2,7 @@
 from .rmsnorm import RMSNorm, ReorderRMSNorm  # noqa: F401
 from .row_parallel import (  # noqa: F401
     FusedRowParallelLinear,
+    HierarchicalRowParallelLinear,
     OverlapRowParallelLayer,
     RowParallelLayer,
 )

@@ -26,7 +26,7 @@ def _rms(x, w, eps):
 
 class TPDecoderBlock(nn.Module):
     def __init__(self, impl, hidden: int = 8192, ffn: int = 28672, n_heads: int = 64, n_kv_heads: int = 8,
-                 eps: float = 1e-5, algo: int = 3, dtype=torch.bfloat16, device=None, seed: int = 0):
+                 eps: float = 1e-5, algo: int = 8, dtype=torch.bfloat16, device=None, seed: int = 0):
         super().__init__()
         self.impl = impl
         self.world = dist.get_world_size() if dist.is_initialized() else 1
@@ -98,8 +98,10 @@ class TPDecoderBlock(nn.Module):
 
     def _fit(self, M, N):
         """The preferred tile configuration if it divides the shape, else a smaller one."""
-        for algo, (bm, bn) in ((self.algo, {0: (128, 256), 1: (128, 128), 2: (128, 64), 3: (256, 256),
-                                            4: (256, 128)}[self.algo]), (1, (128, 128)), (2, (128, 64))):
+        from ..utils.config import ALGO_TILES
+
+        for algo in (self.algo, 3, 0, 1, 2):
+            bm, bn, _ = ALGO_TILES[algo]
             if M % bm == 0 and N % bn == 0:
                 return algo
         raise ValueError(f"no tile configuration divides {M} x {N}")

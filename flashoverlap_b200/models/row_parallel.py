@@ -126,3 +126,78 @@ class FusedRowParallelLinear(nn.Module):
         self.impl.gemm_reducescatter_fused(x, self.weight, out, self.norm_weight, self.eps, self.algo,
                                            self.interleave)
         return out
+
+
+class HierarchicalRowParallelLinear(nn.Module):
+    """Row-parallel linear (+ RMSNorm) over ``nodes x local`` ranks: fused inside
+    a node, NCCL across nodes.
+
+    * inside every node the fused kernel computes the GEMM and reduce-scatters
+      the partial products over NVLink: local rank l ends up with rows
+      ``[l*M/local, (l+1)*M/local)`` summed over its node;
+    * across the nodes the ranks with the same local index sum their slices
+      (``all_reduce`` of M/local rows) or, for a reduce-scatter result,
+      reduce-scatter them so that every rank keeps M/world rows;
+    * RMSNorm runs on the slice each rank holds;
+    * for an all-reduce result the node's ranks all-gather their slices.
+
+    With one node this is :class:`FusedRowParallelLinear` with ``comm_op``
+    ``reduce_scatter`` followed by an all-gather.  ``impl`` must be an
+    ``OverlapImpl`` made for ``hierarchy.intra`` (``make_overlap_impl(group=...)``).
+
+    Row ownership of the reduce-scatter result: rank (node n, local l) holds
+    rows ``l*M/local + n*M/world + [0, M/world)``."""
+
+    def __init__(self, impl, hierarchy, in_features: int, out_features: int, comm_op: str = "all_reduce",
+                 norm: bool = False, eps: float = 1e-5, algo: int = 0, dtype=torch.float16, device=None):
+        super().__init__()
+        assert comm_op in ("all_reduce", "reduce_scatter"), f"unknown comm_op {comm_op!r}"
+        dev = _device(device)
+        self.impl = impl
+        self.h = hierarchy
+        self.comm_op = comm_op
+        self.eps = eps
+        self.algo = algo
+        world = hierarchy.nodes * hierarchy.local_size
+        self.weight = nn.Parameter(torch.randn(out_features, in_features, dtype=dtype, device=dev) /
+                                   (in_features * world) ** 0.5)
+        self.norm_weight: Optional[nn.Parameter] = (
+            nn.Parameter(torch.ones(out_features, dtype=dtype, device=dev)) if norm else None)
+
+    def owned_rows(self, M: int) -> tuple[int, int]:
+        """[begin, end) of the rows a reduce-scatter result holds on this rank."""
+        per_local = M // self.h.local_size
+        per_rank = per_local // self.h.nodes
+        begin = self.h.local_rank * per_local + self.h.node * per_rank
+        return begin, begin + per_rank
+
+    @torch.no_grad()
+    def forward(self, x):
+        h = self.h
+        M, N = x.size(0), self.weight.size(0)
+        rows = M // h.local_size
+        part = torch.empty((rows, N), dtype=x.dtype, device=x.device)
+        # the RMSNorm can only be fused when the node's sum is already the full sum
+        fuse_norm = self.norm_weight is not None and h.nodes == 1
+        self.impl.gemm_reducescatter_fused(x, self.weight, part, self.norm_weight if fuse_norm else None, self.eps,
+                                           self.algo, False)
+        if h.nodes > 1:
+            if self.comm_op == "all_reduce":
+                dist.all_reduce(part, group=h.inter)
+                mine = part
+            else:
+                mine = torch.empty((rows // h.nodes, N), dtype=x.dtype, device=x.device)
+                dist.reduce_scatter_tensor(mine, part, group=h.inter)
+            if self.norm_weight is not None:
+                out = torch.empty_like(mine)
+                torch.ops.flashoverlap_op.rmsnorm(mine, out, self.norm_weight, self.eps)
+                mine = out
+        else:
+            mine = part
+        if self.comm_op == "reduce_scatter":
+            return mine
+        if h.local_size == 1:
+            return mine
+        full = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(full, mine, group=h.intra)
+        return full

@@ -8,3 +8,4 @@ from .bootstrap import (  # noqa: F401
     make_overlap_impl,
     max_over_ranks,
 )
+from .hierarchy import Hierarchy, build_hierarchy, make_intra_node_impl, node_layout  # noqa: F401,E402

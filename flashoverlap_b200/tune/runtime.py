@@ -63,22 +63,42 @@ def usable_algos(M: int, N: int) -> List[int]:
     return [i for i, (bm, bn, _) in enumerate(ALGO_TILES) if M % bm == 0 and N % bn == 0]
 
 
+RASTER_CHOICES = (1, 2, 4, 8)
+
+
 def profile_gemm(impl, M: int, N: int, K: int, dtype=torch.float16, warmup: int = 10, reps: int = 100,
-                 keep: int = 10) -> Tuple[List[int], List[int], List[float], List[int]]:
+                 keep: int = 10, rasters: Sequence[int] = (), with_raster_table: bool = False):
     """Times every tile configuration that fits the shape and returns the
-    ``keep`` fastest as stage-1 lists (reference: tune/profile_config.py:18-74)."""
+    ``keep`` fastest as stage-1 lists ``(BM, BN, dur, Algo)`` (reference:
+    tune/profile_config.py:18-74).  With ``rasters`` every configuration is also
+    timed for those raster groups (how many tile rows the kernel walks together:
+    L2 reuse against how early rows complete); ``dur`` is then the best of them
+    and, with ``with_raster_table``, a fifth value ``{raster: [ms per kept
+    configuration]}`` is returned for the predictive search."""
     A, B, C = make_inputs(M, N, K, dtype)
     rows = []
+    table = {}
     for algo in usable_algos(M, N):
-        ms = mean_time_ms(lambda: impl.cutlass_gemm(A, B, C, algo), warmup, reps)
-        rows.append((ms, algo))
-        dbg(f"profile_gemm: algo {algo} {ALGO_TILES[algo]} {ms:.4f} ms")
+        best = None
+        for rg in (tuple(rasters) or (0,)):
+            impl.set_raster_group(rg)
+            try:
+                ms = mean_time_ms(lambda: impl.cutlass_gemm(A, B, C, algo), warmup, reps)
+            finally:
+                impl.set_raster_group(0)
+            table[(algo, rg)] = ms
+            best = ms if best is None else min(best, ms)
+            dbg(f"profile_gemm: algo {algo} {ALGO_TILES[algo]} raster {rg}: {ms:.4f} ms")
+        rows.append((best, algo))
     if not rows:
         raise ValueError(f"no tile configuration divides M={M}, N={N}")
     rows.sort()
     rows = rows[:keep]
-    return ([ALGO_TILES[a][0] for _, a in rows], [ALGO_TILES[a][1] for _, a in rows], [ms for ms, _ in rows],
-            [a for _, a in rows])
+    out = ([ALGO_TILES[a][0] for _, a in rows], [ALGO_TILES[a][1] for _, a in rows], [ms for ms, _ in rows],
+           [a for _, a in rows])
+    if with_raster_table:
+        return out + ({int(rg): [table[(a, rg)] for _, a in rows] for rg in rasters},)
+    return out
 
 
 def compute_hint(impl, M: int, N: int, K: int, BM: int, BN: int, algo: int, wave_size: int, comm_op: str,

@@ -133,10 +133,12 @@ def predictive_search(impl, M: int, N: int, K: int, comm_op: str, curve: torch.T
         link_gbs = 1.0  # unused with one rank
     data = cfg.load_config(M, N, K, path)
     BM_l, BN_l, dur_l, Algo_l = cfg.stage1_lists(data)
+    by_raster = cfg.stage1_raster_table(data)  # GEMM time per (configuration, raster group), if profiled
     ranked = []
     for t in range(min(10, len(BM_l))):
         for rg in knob_candidates(M, BM_l[t]):
-            est = predict_fused_ms(M, N, dur_l[t], ws, comm_op, link_gbs, transport=link_kind, tile_m=BM_l[t],
+            gemm_ms = by_raster[rg][t] if rg in by_raster else dur_l[t]
+            est = predict_fused_ms(M, N, gemm_ms, ws, comm_op, link_gbs, transport=link_kind, tile_m=BM_l[t],
                                    raster_group=rg)
             ranked.append((est, t, rg))
     ranked.sort()

@@ -5,7 +5,7 @@ tune/search.py:70-102, tune/bandwidth.py:154-155, tool/generate_instances.py:20-
 * ``configs/m{M}n{N}k{K}_{gpu}.json``  stage 1: lists ``BM, BN, dur, Algo`` (fastest GEMM
   tile configurations, ``dur`` in ms); stage 2: scalars ``BM, BN, dur, Algo`` plus
   ``hint`` (tile ids in slot order), ``cSeg`` (tiles per wave group) and ``rLDN``.
-  This library adds optional keys (``raster_group``, ``reduce_group``, ``nvls``,
+  This library adds optional keys (``raster_group``, ``two_stream_dur``, ``candidates_timed``,
   ``fused_dur``, ``stage1``) that the reference's readers ignore.  Stage 2 keeps the
   stage-1 lists under ``stage1`` so that a search can be re-run without re-profiling.
 * ``configs/bandwidth_{op}_tp{ws}.pt`` / ``..._ws{ws}.pt``: float tensor ``[n, 2]`` of
@@ -62,12 +62,20 @@ def json_path(M: int, N: int, K: int, path: Optional[os.PathLike] = None, gpu: O
 
 
 def save_stage1(M: int, N: int, K: int, BM: Sequence[int], BN: Sequence[int], dur: Sequence[float],
-                Algo: Sequence[int], path=None, gpu=None) -> Path:
+                Algo: Sequence[int], path=None, gpu=None, dur_raster: Optional[dict] = None) -> Path:
+    """``dur_raster`` (optional, this library only): ``{raster group: [GEMM ms per
+    listed configuration]}``, what the predictive search uses as the GEMM time
+    of a (configuration, raster group) candidate."""
     if not (len(BM) == len(BN) == len(dur) == len(Algo)) or len(BM) == 0:
         raise ValueError("stage-1 lists must be non-empty and of equal length")
     f = json_path(M, N, K, path, gpu)
     data = {"BM": list(map(int, BM)), "BN": list(map(int, BN)), "dur": list(map(float, dur)),
             "Algo": list(map(int, Algo))}
+    if dur_raster:
+        for rg, col in dur_raster.items():
+            if len(col) != len(BM):
+                raise ValueError("dur_raster columns must be as long as the stage-1 lists")
+        data["dur_raster"] = {str(int(rg)): [float(v) for v in col] for rg, col in dur_raster.items()}
     with open(f, "w", encoding="utf-8") as fh:
         json.dump(data, fh, indent=4)
     return f
@@ -96,6 +104,12 @@ def stage1_lists(data: dict):
         if src is None:  # a stage-2 file written by the reference: one candidate survives
             return [data["BM"]], [data["BN"]], [data["dur"]], [data["Algo"]]
     return list(src["BM"]), list(src["BN"]), list(src["dur"]), list(src["Algo"])
+
+
+def stage1_raster_table(data: dict) -> dict:
+    """``{raster group: [GEMM ms per stage-1 configuration]}`` if the profile recorded it, else {}."""
+    src = data if isinstance(data["BM"], list) else (data.get("stage1") or {})
+    return {int(rg): list(col) for rg, col in (src.get("dur_raster") or {}).items()}
 
 
 def is_stage2(data: dict) -> bool:
@@ -129,7 +143,8 @@ def save_stage2(M: int, N: int, K: int, BM: int, BN: int, dur: float, Algo: int,
         with open(f, "r", encoding="utf-8") as fh:
             data = json.load(fh)
     if isinstance(data.get("BM"), list):
-        data["stage1"] = {k: data[k] for k in ("BM", "BN", "dur", "Algo")}
+        data["stage1"] = {k: data[k] for k in ("BM", "BN", "dur", "Algo", "dur_raster") if k in data}
+        data.pop("dur_raster", None)
     data.update({"hint": [int(h) for h in hint], "cSeg": [int(c) for c in cSeg], "rLDN": 1, "BM": int(BM),
                  "BN": int(BN), "dur": float(dur), "Algo": int(Algo)})
     data.update(extra)

@@ -9,9 +9,11 @@ For every shape and both collectives the script
 1. times this library's GEMM for the candidate tile configurations (stage 1),
 2. exhaustive: times the fused kernel for every (tile configuration, raster
    group) candidate and keeps the best,
-3. predictive: ranks the same candidates with the cost model on the link
-   bandwidth MEASURED at the start of the run (the library's own transport, 64 MiB
-   messages) and times only the model's first pick,
+3. predictive: ranks the same candidates with the cost model on the GEMM times
+   of step 1 and the link bandwidth MEASURED at the start of the run (the
+   library's own transport, 64 MiB messages) and times only the model's first
+   pick; when the picks differ both are timed again in alternation and the gap
+   is the ratio of those times,
 4. times the non-overlapped baseline (cuBLAS GEMM, one NCCL collective, RMSNorm
    kernel) in alternation with the best fused configuration.
 
@@ -42,7 +44,7 @@ def measure_link(impl, ws, reps=10):
     if ws == 1:
         return 1.0, "p2p"
     total = 64 << 20
-    if impl.nvls_available():
+    if impl.allreduce_uses_nvls():
         ms = mean_time_ms(lambda: impl.multimem_bench("allreduce", total, 0, False), 3, reps)
         return total * (1 + 1 / ws) / (ms * 1e-3) / 1e9, "nvls"
     per_peer = total // (ws - 1) // 16 * 16
@@ -58,7 +60,7 @@ def main():
     ap.add_argument("--dtype", default="float16", choices=sorted(DTYPES))
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--search_reps", type=int, default=5)
-    ap.add_argument("--algos", type=int, nargs="+", default=[0, 3, 4], help="tile configurations to consider")
+    ap.add_argument("--algos", type=int, nargs="+", default=[0, 3, 8], help="tile configurations to consider")
     ap.add_argument("--jsonl", default=None)
     ap.add_argument("--md", default=None, help="write a markdown table here (rank 0)")
     args = ap.parse_args()
@@ -88,8 +90,14 @@ def main():
                 DO = torch.empty_like(D)
                 algos = [a for a in args.algos if M % ALGO_TILES[a][0] == 0 and N % ALGO_TILES[a][1] == 0
                          and (M // ws) % ALGO_TILES[a][0] == 0]
-                gemm_ms = {a: mean_time_ms(lambda a=a: impl.cutlass_gemm(A, B, C, a), 3, args.search_reps, flush=True)
-                           for a in algos}
+                def gemm_time(a, rg):  # stage 1: the GEMM alone for every (tile configuration, raster group)
+                    impl.set_raster_group(rg)
+                    try:
+                        return mean_time_ms(lambda: impl.cutlass_gemm(A, B, C, a), 3, args.search_reps, flush=True)
+                    finally:
+                        impl.set_raster_group(0)
+
+                gemm_ms = {(a, rg): gemm_time(a, rg) for a in algos for rg in knob_candidates(M, ALGO_TILES[a][0])}
                 for op in ("all_reduce", "reduce_scatter"):
                     def fused(a):
                         if op == "all_reduce":
@@ -108,11 +116,21 @@ def main():
                     times = {c: timed(*c) for c in cands}                       # exhaustive: everything is timed
                     ex = min(times, key=times.get)
                     kind = link_kind if op == "all_reduce" else "p2p"
-                    pred = {c: predict_fused_ms(M, N, gemm_ms[c[0]], ws, op, link_gbs, transport=kind,
+                    pred = {c: predict_fused_ms(M, N, gemm_ms[c], ws, op, link_gbs, transport=kind,
                                                 tile_m=ALGO_TILES[c[0]][0], raster_group=c[1]) for c in cands}
                     pr = min(pred, key=pred.get)
                     pr_ms = timed(*pr)                                          # predictive: only its pick is timed
-                    gap = pr_ms / times[ex] - 1.0
+                    if pr == ex:
+                        gap = 0.0
+                    else:
+                        # both picks again, in alternation, so that clock and power drift do not decide the comparison
+                        def run_pick(c):
+                            impl.set_raster_group(c[1])
+                            fused(c[0])
+
+                        tp_, te_ = time_pairs(lambda: run_pick(pr), lambda: run_pick(ex), args.steps, 2)
+                        impl.set_raster_group(0)
+                        gap = max_over_ranks(sum(tp_)) / max_over_ranks(sum(te_)) - 1.0
 
                     def b_step():
                         if op == "all_reduce":

@@ -76,6 +76,20 @@ def main():
         layer_rs = RowParallelLayer(K, N, "reduce_scatter", None, dtype=torch.float32, device="cpu")
         layer_rs.weight.copy_(B)
         check("RowParallelLayer(reduce_scatter)", layer_rs(A), full[blk])
+    # two-level groups for jobs on several nodes: the ranks cut into pretend nodes
+    from flashoverlap_b200.parallel import build_hierarchy
+
+    os.environ["FLASHOVERLAP_FAKE_NODES"] = str(world)  # every rank its own node
+    h = build_hierarchy()
+    assert (h.nodes, h.local_size, h.node, h.local_rank) == (world, 1, rank, 0) and h.intra is None
+    if world > 1:
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, group=h.inter)
+        assert float(t) == world * (world + 1) / 2
+    os.environ["FLASHOVERLAP_FAKE_NODES"] = "1"  # one node holding every rank
+    h = build_hierarchy()
+    assert (h.nodes, h.local_size, h.node, h.local_rank) == (1, world, 0, rank) and h.inter is None
+    del os.environ["FLASHOVERLAP_FAKE_NODES"]
     # control-plane helpers
     assert max_over_ranks(float(rank)) == float(world - 1)
     ids = broadcast_nccl_id() if world == 1 else None  # NCCL ids need the native library + GPU; world 1 path only

@@ -14,7 +14,7 @@ import torch  # noqa: E402
 
 from flashoverlap_b200.cli import DTYPES  # noqa: E402
 
-from flashoverlap_b200.tune.runtime import profile_gemm
+from flashoverlap_b200.tune.runtime import RASTER_CHOICES, profile_gemm
 from flashoverlap_b200.utils import config as cfg
 
 
@@ -30,9 +30,10 @@ def main():
     cfg.save_algo_dict(args.path)
     impl = torch.classes.flashoverlap_class.OverlapImpl()
     impl.cutlass_init()
-    BM, BN, dur, algo = profile_gemm(impl, args.m, args.n, args.k, DTYPES[args.dtype])
+    BM, BN, dur, algo, by_raster = profile_gemm(impl, args.m, args.n, args.k, DTYPES[args.dtype],
+                                                rasters=RASTER_CHOICES, with_raster_table=True)
     impl.check_status()
-    f = cfg.save_stage1(args.m, args.n, args.k, BM, BN, dur, algo, args.path)
+    f = cfg.save_stage1(args.m, args.n, args.k, BM, BN, dur, algo, args.path, dur_raster=by_raster)
     for row in zip(algo, BM, BN, dur):
         print("Algo %d  %dx%d  %.4f ms" % row)
     print(f"saved {f}")
