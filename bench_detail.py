@@ -28,9 +28,14 @@ def rel_err(got, want):
     return (got - want.float()).abs().max().item() / max(1.0, want.float().abs().max().item())
 
 
+def med_ratio(base_ts, fused_ts):
+    """Ratio of the median step times: what one slow step (a stray clock dip) does not move."""
+    return round(statistics.median(base_ts) / statistics.median(fused_ts), 3)
+
+
 def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     from flashoverlap_b200.parallel import make_baseline_impl
-    from flashoverlap_b200.tune.runtime import search_two_stream
+    from flashoverlap_b200.tune.runtime import gather_algo_candidates, pick_algo_by_timing, search_two_stream
     from flashoverlap_b200.utils.config import ALGO_TILES
     from flashoverlap_b200.utils.reorder import generate_row_mapping, reorder_indices
     from flashoverlap_b200.utils.timing import time_pairs, time_steps
@@ -70,7 +75,8 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     gt, ct = time_pairs(lambda: impl.cutlass_gemm(x, W, C, algo), lambda: base.cublas_gemm(x, W, C), steps, warmup)
     detail["ar_fp16"] = {
         "fused_ms": round(fused_ms, 4), "nccl_baseline_ms": round(base_ms, 4),
-        "speedup_vs_nccl_baseline": round(base_ms / fused_ms, 3), "measured": "alternating steps",
+        "speedup_vs_nccl_baseline": round(base_ms / fused_ms, 3), "speedup_of_medians": med_ratio(bt, ft),
+        "measured": "alternating steps",
         "fused_per_step_ms": stats(ft), "baseline_per_step_ms": stats(bt),
         "own_gemm_ms": round(mean_max(gt), 4), "cublas_gemm_ms": round(mean_max(ct), 4),
     }
@@ -138,7 +144,8 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     rs_ms, base_rs_ms = sum(rt) / steps, sum(brt) / steps
     detail["rs_bf16"] = {
         "M": M2, "N": N2, "K_per_rank": K2, "fused_ms": round(rs_ms, 4), "nccl_baseline_ms": round(base_rs_ms, 4),
-        "speedup_vs_nccl_baseline": round(base_rs_ms / rs_ms, 3), "fused_per_step_ms": stats(rt),
+        "speedup_vs_nccl_baseline": round(base_rs_ms / rs_ms, 3), "speedup_of_medians": med_ratio(brt, rt),
+        "fused_per_step_ms": stats(rt), "baseline_per_step_ms": stats(brt),
         "tflops": round(2.0 * M2 * N2 * K2_total / (rs_ms * 1e-3) / 1e12, 1),
     }
     fused_rs()
@@ -163,8 +170,15 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     Cb = torch.empty(Mq, Nq, device=dev, dtype=bf)
     gathered = torch.empty(Mq, Kq, device=dev, dtype=bf)
 
+    # the tile configuration of a gather operation is searched like the tuner's stage 1: a few candidates
+    # ranked by tiles per source block, each timed briefly, fastest kept
+    ag_algo, ag_timed = algo, []
+    if world > 1:
+        cands = list(dict.fromkeys([algo] + gather_algo_candidates(Mq // world, Nq)[:3]))
+        ag_algo, ag_timed = pick_algo_by_timing(lambda a: impl.allgather_gemm(shard, Bq, Cq, a), cands)
+
     def fused_ag():
-        impl.allgather_gemm(shard, Bq, Cq, algo)
+        impl.allgather_gemm(shard, Bq, Cq, ag_algo)
 
     def base_ag():
         if world > 1:
@@ -179,8 +193,10 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     push_bytes = (world - 1) * shard.numel() * 2
     detail["allgather_gemm_bf16"] = {
         "M": Mq, "N_per_rank": Nq, "K": Kq, "fused_ms": round(ag_ms, 4), "nccl_plus_cublas_ms": round(base_ag_ms, 4),
-        "speedup": round(base_ag_ms / ag_ms, 3), "fused_per_step_ms": stats(at),
+        "speedup": round(base_ag_ms / ag_ms, 3), "speedup_of_medians": med_ratio(bat, at),
+        "fused_per_step_ms": stats(at), "baseline_per_step_ms": stats(bat),
         "push_gbs_lower_bound": round(push_bytes / (ag_ms * 1e-3) / 1e9, 1) if world > 1 else 0.0,
+        "algo": ag_algo, "algos_timed": [{"algo": a, "ms": round(t, 4)} for a, t in ag_timed],
     }
     fused_ag()
     torch.cuda.synchronize()
@@ -198,7 +214,7 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     send = (torch.randn(T, Ke, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)) / Ke ** 0.5
             ).to(torch.float16)
     Be = (torch.randn(Ne, Ke, device=dev) / Ke ** 0.5).to(torch.float16)
-    m_pad = impl.a2a_padded_rows(mlen, algo)
+    m_pad = (impl.a2a_padded_rows(mlen, algo) + 255) // 256 * 256  # room for every tile height
     Ce = torch.empty(m_pad, Ne, device=dev, dtype=torch.float16)
     recv_rows = int(mlen[:, rank].sum())
     recv = torch.empty(recv_rows, Ke, device=dev, dtype=torch.float16)
@@ -206,8 +222,13 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     in_split = [int(v) for v in mlen[rank]]
     out_split = [int(v) for v in mlen[:, rank]]
 
+    e_algo, e_timed = algo, []
+    if world > 1:
+        cands = list(dict.fromkeys([algo] + gather_algo_candidates(T // world, Ne)[:3]))
+        e_algo, e_timed = pick_algo_by_timing(lambda a: impl.a2a_dispatch_gemm(send, Be, Ce, mlen, a), cands)
+
     def fused_a2a():
-        impl.a2a_dispatch_gemm(send, Be, Ce, mlen, algo)
+        impl.a2a_dispatch_gemm(send, Be, Ce, mlen, e_algo)
 
     def base_a2a():
         if world > 1:
@@ -221,7 +242,9 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     detail["a2a_gemm_fp16"] = {
         "tokens_per_rank": T, "K": Ke, "N": Ne, "recv_rows_min_max": [int(mlen.sum(0).min()), int(mlen.sum(0).max())],
         "fused_ms": round(sum(et) / steps, 4), "nccl_plus_cublas_ms": round(sum(bet) / steps, 4),
-        "speedup": round(sum(bet) / sum(et), 3), "fused_per_step_ms": stats(et),
+        "speedup": round(sum(bet) / sum(et), 3), "speedup_of_medians": med_ratio(bet, et),
+        "fused_per_step_ms": stats(et), "baseline_per_step_ms": stats(bet),
+        "algo": e_algo, "algos_timed": [{"algo": a, "ms": round(t, 4)} for a, t in e_timed],
     }
     fused_a2a()
     base_a2a()

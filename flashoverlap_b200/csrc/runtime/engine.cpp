@@ -415,6 +415,18 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
   const int rows = M / world_;
   if (rows % 128 != 0) throw std::runtime_error("allgather_gemm: M / world must be a multiple of 128");
   if (K % 8 != 0) throw std::runtime_error("allgather_gemm: K must be a multiple of 8");
+  if (world_ == 1 && reinterpret_cast<uintptr_t>(A_shard) % 16 == 0) {  // nothing to gather: the GEMM reads the caller's matrix
+    GemmOperands g{};
+    g.A = A_shard;
+    g.B = B;
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.dtype = dtype;
+    g.algo = algo;
+    gemm(g, C, nullptr, nullptr, stream);
+    return;
+  }
   ensure_workspace(static_cast<long long>(M) * (K > N ? K : N), 1);
   const int set = static_cast<int>(calls_ & 1ull);
   const size_t shard_bytes = static_cast<size_t>(rows) * K * 2;
@@ -452,6 +464,18 @@ void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int
     if (mlen[i] < 0) throw std::runtime_error("a2a_gemm: negative row count");
   }
   const int m_pad = a2a_padded_rows(mlen, algo);  // the same on every rank
+  if (world_ == 1 && mlen[0] == m_pad && reinterpret_cast<uintptr_t>(A_send) % 16 == 0) {  // one rank, whole tiles: in place
+    GemmOperands g{};
+    g.A = A_send;
+    g.B = B;
+    g.M = m_pad;
+    g.N = N;
+    g.K = K;
+    g.dtype = dtype;
+    g.algo = algo;
+    gemm(g, C, nullptr, nullptr, stream);
+    return;
+  }
   ensure_workspace(static_cast<long long>(m_pad) * (K > N ? K : N), 1);
   const int set = static_cast<int>(calls_ & 1ull);
   const size_t row_bytes = static_cast<size_t>(K) * 2;

@@ -93,7 +93,7 @@ class TPDecoderBlock(nn.Module):
         n = torch.empty_like(h3)
         torch.ops.flashoverlap_op.rmsnorm(h3, n, self.norm_next, self.eps)
         qkv_next = torch.empty((T, self.w_qkv_next.shape[0]), dtype=h3.dtype, device=h3.device)
-        impl.allgather_gemm(n, self.w_qkv_next, qkv_next, self._fit(T, self.w_qkv_next.shape[0]))  # all-gather + GEMM
+        impl.allgather_gemm(n, self.w_qkv_next, qkv_next, self._fit_gather(T, self.w_qkv_next.shape[0]))  # all-gather + GEMM
         return qkv_next, h3
 
     def _fit(self, M, N):
@@ -105,6 +105,19 @@ class TPDecoderBlock(nn.Module):
             if M % bm == 0 and N % bn == 0:
                 return algo
         raise ValueError(f"no tile configuration divides {M} x {N}")
+
+    def _fit_gather(self, M, N):
+        """Tile configuration of the all-gather GEMM: the gathered rows are consumed
+        shard by shard, so the tile is chosen for the tiles ONE shard gives."""
+        from ..tune.model import gather_algo_candidates
+        from ..utils.config import ALGO_TILES
+
+        if self.world == 1:
+            return self._fit(M, N)
+        for algo in gather_algo_candidates(M // self.world, N):
+            if M % ALGO_TILES[algo][0] == 0:
+                return algo
+        return self._fit(M, N)
 
     # ---- PyTorch path -------------------------------------------------------
     @torch.no_grad()

@@ -210,3 +210,36 @@ def predict_fused_ms(M: int, N: int, gemm_ms: float, world_size: int, comm_op: s
     tail_rows = min(M, tile_m * max(raster_group, 1))
     tail_ms = comm_ms * tail_rows / M + latency_us * 1e-3
     return max(gemm_ms, comm_ms * (1.0 - tail_rows / M)) + tail_ms
+
+
+def _algo_tiles():
+    from ..utils.config import ALGO_TILES
+
+    return ALGO_TILES
+
+
+def gather_algo_candidates(rows_per_source: int, n: int, sms: int = 148) -> List[int]:
+    """Tile configurations worth timing for all-gather -> GEMM and all-to-all
+    dispatch -> GEMM.  The GEMM consumes the gathered matrix source by source
+    as the blocks arrive, so what matters is how many tiles ONE source's block
+    gives: a block of 1024 rows and 1280 columns is 20 tiles of 256 x 256 (a
+    quarter of the machine busy per step) but 80 tiles of 128 x 128.  Returns
+    the configurations ordered by the estimated time per block, best first:
+    waves needed for the block's tiles times the area of a tile, with small
+    tiles charged for their lower tensor-core efficiency."""
+    rows = max(int(rows_per_source), 1)
+    penalty = {256 * 256: 1.0, 256 * 128: 1.08, 128 * 256: 1.08, 128 * 128: 1.2, 256 * 64: 1.3, 128 * 64: 1.5}
+    scored = []
+    for algo, (bm, bn, bk) in enumerate(_algo_tiles()):
+        if bk != 128 and (bm, bn) != (128, 256):   # one K depth per tile shape
+            continue
+        if n % bn:
+            continue
+        ctas = bm // 128
+        tiles = -(-rows // bm) * (n // bn)
+        slots = max(1, sms // ctas)
+        waves = -(-tiles // slots)
+        per_tile = bm * bn / ctas * penalty.get(bm * bn, 1.5)
+        scored.append((waves * per_tile, -bm * bn, algo))
+    scored.sort()
+    return [a for _, _, a in scored]

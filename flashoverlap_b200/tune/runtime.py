@@ -15,7 +15,7 @@ from ..parallel import make_overlap_impl, max_over_ranks
 from ..utils.config import ALGO_TILES
 from ..utils.reorder import generate_row_mapping, reorder_indices
 from ..utils.timing import flush_l2
-from .model import div_up, hint_from_samples
+from .model import div_up, gather_algo_candidates, hint_from_samples  # noqa: F401
 
 
 def dbg(msg: str) -> None:
@@ -263,3 +263,16 @@ def search_two_stream(impl, M: int, N: int, K: int, algo: int, comm_op: str, dty
         timed.append((g, ms))
     best = min(timed, key=lambda t: t[1])
     return best[0], best[1], timed
+
+
+def pick_algo_by_timing(run: Callable[[int], None], algos: Sequence[int], warmup: int = 2, reps: int = 5):
+    """Times ``run(algo)`` for every candidate (L2 flushed, slowest rank) and
+    returns ``(best algo, [(algo, ms), ...])``: the stage-1 search of the
+    tuner for operations whose best tile depends on the ranks' arrival pattern
+    (reference: tune/profile_config.py times every instance and keeps the
+    fastest)."""
+    timed = []
+    for a in algos:
+        timed.append((a, mean_time_ms(lambda: run(a), warmup, reps, flush=True)))
+    best = min(timed, key=lambda t: t[1])[0]
+    return best, timed

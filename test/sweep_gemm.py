@@ -26,6 +26,8 @@ def main():
     ap.add_argument("--k", type=int, nargs="+", default=[1024, 4096, 8192])
     ap.add_argument("--dtype", default="float16", choices=sorted(DTYPES))
     ap.add_argument("--reps", type=int, default=50)
+    ap.add_argument("--rasters", type=int, nargs="+", default=[0],
+                    help="raster groups (tile rows walked together) to try per tile; 0 = the library's default")
     ap.add_argument("--jsonl", default=None)
     args = ap.parse_args()
     torch.cuda.set_device(0)
@@ -39,16 +41,22 @@ def main():
             for K in args.k:
                 A, B, C = make_inputs(M, N, K, DTYPES[args.dtype])
                 t_vendor = mean_time_ms(lambda: base.cublas_gemm(A, B, C), 10, args.reps)
-                best = min((mean_time_ms(lambda a=a: impl.cutlass_gemm(A, B, C, a), 10, args.reps), a)
-                           for a in usable_algos(M, N))
+                timed = []
+                for rg in args.rasters:
+                    impl.set_raster_group(rg)
+                    timed += [(mean_time_ms(lambda a=a: impl.cutlass_gemm(A, B, C, a), 10, args.reps), a, rg)
+                              for a in usable_algos(M, N)]
+                impl.set_raster_group(0)
+                best = min(timed)
                 tf = 2.0 * M * N * K / (best[0] * 1e-3) / 1e12
                 tile = cfg.ALGO_TILES[best[1]]
                 print(f"{M:>6} {N:>6} {K:>6} | {t_vendor:>10.4f} {best[0]:>10.4f} {best[0] / t_vendor:>6.2f} {tf:>8.0f}"
-                      f"  {tile[0]}x{tile[1]}")
+                      f"  {tile[0]}x{tile[1]}x{tile[2]}" + (f" raster {best[2]}" if best[2] else ""))
                 if args.jsonl:
                     with open(args.jsonl, "a") as fh:
                         fh.write(json.dumps({"M": M, "N": N, "K": K, "dtype": args.dtype, "vendor_ms": t_vendor,
-                                             "own_ms": best[0], "algo": best[1], "tflops": tf}) + "\n")
+                                             "own_ms": best[0], "algo": best[1], "raster_group": best[2],
+                                             "tflops": tf}) + "\n")
     impl.check_status()
 
 

@@ -253,6 +253,15 @@ def test_a2a_dispatch_gemm_world1():
     assert (C[:300].float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item()
     with pytest.raises(RuntimeError):
         impl.a2a_dispatch_gemm(A[:100], B, C, mlen, 0)  # fewer rows than mLen says
+    # whole tiles on one rank: the GEMM reads the caller's rows in place
+    mlen2 = torch.tensor([[384]], dtype=torch.int32)
+    A2 = torch.randn(384, K, device="cuda", dtype=torch.float16)
+    C.fill_(float("nan"))
+    impl.a2a_dispatch_gemm(A2, B, C, mlen2, 0)
+    torch.cuda.synchronize()
+    impl.check_status()
+    ref2 = A2.float() @ B.float().t()
+    assert (C.float() - ref2).abs().max().item() <= 1e-2 * ref2.abs().max().item()
 
 
 def test_host_feeder_double_buffers_inputs():

@@ -87,3 +87,27 @@ def test_predictive_search_needs_a_measured_link_bandwidth(patched):
     curve = torch.tensor([[2.0 ** 20, 150.0], [2.0 ** 26, 420.0]])
     with pytest.raises(ValueError, match="measured link bandwidth"):
         search.predictive_search(None, M, N, K, "all_reduce", curve, None, path=path, verbose=False)
+
+
+def test_gather_algo_candidates_prefer_tiles_that_fill_the_machine():
+    from flashoverlap_b200.tune.runtime import gather_algo_candidates
+    from flashoverlap_b200.utils.config import ALGO_TILES
+
+    # 1024 rows per source, 1280 columns: 256x256 gives 20 tiles per block, too few for 74 CTA pairs
+    first = ALGO_TILES[gather_algo_candidates(1024, 1280)[0]]
+    assert first[0] * first[1] < 256 * 256
+    # a block that fills the machine several times over keeps the large tile
+    assert ALGO_TILES[gather_algo_candidates(8192, 10240)[0]][:2] == (256, 256)
+    # only tile widths that divide N are offered
+    assert all(1280 % ALGO_TILES[a][1] == 0 for a in gather_algo_candidates(1024, 1280))
+    assert all(ALGO_TILES[a][1] == 64 for a in gather_algo_candidates(512, 192))
+
+
+def test_pick_algo_by_timing_keeps_the_fastest(monkeypatch):
+    from flashoverlap_b200.tune import runtime
+
+    cost = {0: 3.0, 6: 1.0, 9: 2.0}
+    calls = []
+    monkeypatch.setattr(runtime, "mean_time_ms", lambda fn, w, r, flush=False: (fn(), cost[calls[-1]])[1])
+    best, timed = runtime.pick_algo_by_timing(lambda a: calls.append(a), [0, 6, 9])
+    assert best == 6 and [a for a, _ in timed] == [0, 6, 9]
