@@ -40,7 +40,7 @@ CUDA_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-] + (["-DFO_ROW_STAMPS"] if os.environ.get("FO_ROW_STAMPS") else [])
+]
 
 
 def library_path() -> Path:

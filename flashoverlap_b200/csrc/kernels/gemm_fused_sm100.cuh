@@ -375,22 +375,12 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   bool have = false;  // `pre` holds the (summed) chunks of row lr, loaded during the previous iteration
   uint4 pre[CPT];
 
-#ifdef FO_ROW_STAMPS
-  unsigned long long* dbg = (p.phase_trace != nullptr && blockIdx.x == 5 && leader)
-                                ? p.phase_trace + static_cast<unsigned long long>(kTraceWords) * gridDim.x + group * 128
-                                : nullptr;
-#define FO_STAMP(k) if (dbg != nullptr && it < 16) dbg[it * 8 + (k)] = ptx::globaltimer_ns();
-#else
-#define FO_STAMP(k)
-#endif
   for (int it = 0; lr < rows_local; ++it) {
     const int par = it & 1;
-    FO_STAMP(0)
     const int g = global_row(lr);
     const int out_row = p.bcast ? g : lr;
     const uint16_t* src0 = partials_of(lr, g);
     const uint32_t ok = have ? 1u : wait_block(g / BM);
-    FO_STAMP(1)
 
     // ---- sum of the partial rows (and the sum of squares) ----
     uint4 h[CPT];
@@ -457,7 +447,6 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       }
     }
 
-    FO_STAMP(2)
     // ---- one barrier: exchange the partial sums of squares, learn the next row ----
     if (p.norm) {
 #pragma unroll
@@ -474,7 +463,6 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       for (int w = 0; w < kGroupWarps; ++w) ssq += gs->ssq[par][w];
     }
 
-    FO_STAMP(3)
     // ---- the next row's loads go out before this row is stored, if its partials are there ----
     have = false;
     if constexpr (PREFETCH) {
@@ -496,7 +484,6 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       }
     }
 
-    FO_STAMP(4)
     // ---- RMSNorm scaling and delivery of this row ----
     if (p.norm && ok) {
       const float rstd = rsqrtf(ssq / static_cast<float>(p.N) + p.eps);
@@ -516,7 +503,6 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         }
       }
     }
-    FO_STAMP(5)
     // Delivery counts are only read at the end of the kernel, and a release
     // at system scope waits for this warp's stores to be acknowledged by the
     // peers: signal a batch of rows at a time.
@@ -657,6 +643,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
       // not again before the next group (dropped first).
       const uint64_t pol_a = ptx::l2_policy_evict_last();
       const uint64_t pol_b = ptx::l2_policy_evict_first();
+      const int own_begin = p.me == 0 ? 0 : p.a_src_end[p.me - 1];  // gathered A: this rank's own rows
+      const int own_end = p.a_src_end[p.me];
       for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         int m_blk, n_blk;
         tile_coords(p, t, m_blk, n_blk);
@@ -679,6 +667,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           }
           if (!ok) break;
           ptx::fence_proxy_async_all();
+          if (p.phase_trace != nullptr && (a_row < own_begin || a_row >= own_end)) {
+            // first tile of this CTA that needed rows of another rank: when it could start
+            unsigned long long* tr = p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x;
+            if (tr[4] == ~0ull) tr[4] = ptx::globaltimer_ns();
+          }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, deadline)) {
@@ -1021,6 +1014,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
           ptx::fence_acq_rel_sys();
           ptx::red_relaxed_sys_add(p.ag_flag[d], 1u);
         }
+      }
+      if (p.phase_trace != nullptr && lane == 0) {  // when this CTA's share of the push was out
+        atomicMax(p.phase_trace + static_cast<unsigned long long>(kTraceWords) * blockIdx.x + 2, ptx::globaltimer_ns());
       }
       return;
     }

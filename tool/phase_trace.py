@@ -4,8 +4,10 @@ A profiler cannot replay a kernel that waits for other ranks, so the fused
 kernels can record their own timeline (``OverlapImpl.set_phase_trace``): per
 CTA the kernel start, the end of the GEMM phase, the first and the last row
 this CTA reduced and, for an all-reduce, the moment every row had been
-delivered to this rank.  This tool runs the named shapes with the trace on and
-prints one line per rank (microseconds after the kernel start).
+delivered to this rank; for all-gather -> GEMM the moment this rank's pushes
+were out and the moment the first tile that needs another rank's rows could
+start.  This tool runs the named shapes with the trace on and prints one line
+per rank (microseconds after the kernel start).
 
     torchrun --nproc_per_node=8 tool/phase_trace.py [--md profiles/x.md]
 """
@@ -27,9 +29,63 @@ SHAPES = [  # (name, op, M, N, K before the split, dtype)
 ]
 
 
+def gather_trace(impl, rank, ws, sms, args):
+    """All-gather -> GEMM on the decoder block's QKV shape (M 8192 tokens, K 8192, N 10240 / ranks, bf16)."""
+    from flashoverlap_b200.tune.model import gather_algo_candidates
+    from flashoverlap_b200.utils.config import ALGO_TILES
+
+    M, K, N = 8192, 8192, 10240 // ws
+    algo = args.ag_algo if args.ag_algo >= 0 else (gather_algo_candidates(M // ws, N)[0] if ws > 1 else args.algo)
+    dt = torch.bfloat16
+    shard = (torch.randn(M // ws, K, device="cuda") / K ** 0.5).to(dt)
+    full = (torch.randn(M, K, device="cuda") / K ** 0.5).to(dt)
+    B = (torch.randn(N, K, device="cuda") / K ** 0.5).to(dt)
+    C = torch.empty(M, N, device="cuda", dtype=dt)
+    ts = time_steps(lambda: impl.allgather_gemm(shard, B, C, algo), 10, 3)
+    tg = time_steps(lambda: impl.cutlass_gemm(full, B, C, algo), 10, 3)
+    trace = torch.zeros(8 * sms, dtype=torch.int64, device="cuda")
+    impl.set_phase_trace(trace)
+    flush_l2()
+    if ws > 1:
+        dist.barrier()
+    impl.allgather_gemm(shard, B, C, algo)
+    torch.cuda.synchronize()
+    impl.set_phase_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
+    impl.check_status()
+    t = trace.view(sms, 8).cpu()
+    t0 = t[:, 0].min()
+    ge = (t[:, 1] - t0).double() / 1e3
+    push = ((t[:, 2] - t0).double() / 1e3).max().item() if (t[:, 2] > 0).any() else float("nan")
+    started = t[:, 4][(t[:, 4] > 0) & (t[:, 4] != -1)]  # -1 = never waited for a remote row
+    first_remote = (started.min() - t0).item() / 1e3 if started.numel() else float("nan")
+    row = torch.tensor([sorted(ts)[len(ts) // 2] * 1e3, sorted(tg)[len(tg) // 2] * 1e3, push, first_remote,
+                        ge.min().item(), ge.median().item(), ge.max().item()], dtype=torch.float64, device="cuda")
+    rows = [torch.zeros_like(row) for _ in range(ws)]
+    if ws > 1:
+        dist.all_gather(rows, row)
+    else:
+        rows = [row]
+    out = []
+    if rank == 0:
+        tile = ALGO_TILES[algo]
+        sent = (ws - 1) * shard.numel() * 2 / 1e6
+        out.append(f"\n### all-gather -> GEMM bf16 M{M} K{K} N{N} per rank, TP={ws}, Algo {algo} "
+                   f"({tile[0]}x{tile[1]}x{tile[2]}), {sent:.0f} MB pushed per rank\n")
+        out.append("| rank | fused (us, events) | GEMM alone on gathered rows | own pushes out | first tile on remote rows "
+                   "starts | GEMM phase ends min / median / max | push GB/s (sent / time of the pushes) |\n"
+                   "|---|---|---|---|---|---|---|")
+        for r, v in enumerate(rows):
+            v = v.tolist()
+            gbs = sent * 1e6 / (v[2] * 1e-6) / 1e9 if v[2] == v[2] and v[2] > 0 else float("nan")
+            out.append(f"| {r} | {v[0]:.0f} | {v[1]:.0f} | {v[2]:.0f} | {v[3]:.0f} | {v[4]:.0f} / {v[5]:.0f} / {v[6]:.0f} | "
+                       f"{gbs:.0f} |")
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--algo", type=int, default=8)
+    ap.add_argument("--ag_algo", type=int, default=-1, help="tile configuration of the all-gather GEMM (-1: by model)")
     ap.add_argument("--md", default=None)
     args = ap.parse_args()
     rank, ws = start()
@@ -86,6 +142,7 @@ def main():
                 v = v.tolist()
                 lines.append(f"| {r} | {v[0]:.0f} | {v[1]:.0f} | {v[2]:.0f} / {v[3]:.0f} / {v[4]:.0f} | {v[5]:.0f} | "
                              f"{v[6]:.0f} | {v[7]:.0f} |")
+    lines += gather_trace(impl, rank, ws, sms, args)
     if rank == 0:
         text = "\n".join(lines) + "\n"
         print(text)
