@@ -150,6 +150,7 @@ TORCH_LIBRARY(flashoverlap_class, m) {
       .def("set_l2_hints", &OverlapImpl::SetL2Hints)
       .def("set_raster_taper", &OverlapImpl::SetRasterTaper)
       .def("set_phase_trace", &OverlapImpl::SetPhaseTrace)
+      .def("set_row_trace", &OverlapImpl::SetRowTrace)
       .def("status", &OverlapImpl::Status)
       .def("status_string", &OverlapImpl::StatusString)
       .def("check_status", &OverlapImpl::CheckStatus)

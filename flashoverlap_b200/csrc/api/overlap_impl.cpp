@@ -684,6 +684,18 @@ void OverlapImpl::SetPhaseTrace(at::Tensor buf) {
   engine_.set_phase_trace(reinterpret_cast<unsigned long long*>(buf.data_ptr<int64_t>()));
 }
 
+void OverlapImpl::SetRowTrace(at::Tensor buf) {
+  if (buf.numel() == 0) {
+    engine_.set_row_trace(nullptr, 0);
+    row_trace_ = at::Tensor();
+    return;
+  }
+  TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && buf.scalar_type() == at::kLong && buf.numel() % 6 == 0,
+              "row trace buffer must be a contiguous CUDA int64 tensor of 6 * rows entries");
+  row_trace_ = buf;  // keeps the memory alive
+  engine_.set_row_trace(reinterpret_cast<unsigned long long*>(buf.data_ptr<int64_t>()), buf.numel() / 6);
+}
+
 std::vector<int64_t> OverlapImpl::Status() {
   StatusWord s = engine_.read_status();
   return {s.code, s.rank, s.where, s.seen, s.want};

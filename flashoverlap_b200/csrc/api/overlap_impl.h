@@ -127,6 +127,10 @@ class OverlapImpl : public torch::CustomClassHolder {
   // (int64, at least 8 * SM count entries, layout in FusedParams::phase_trace;
   // an empty tensor turns it off).
   void SetPhaseTrace(at::Tensor buf);
+  // Every following fused launch whose M is at most rows records a timeline of
+  // its reduce phase into `buf` (int64 [6, rows]: claimed, stored, CTA * 4 +
+  // row group, partials there, summed, barrier passed; times as %globaltimer ns; an empty tensor turns it off).
+  void SetRowTrace(at::Tensor buf);
   // [code, rank, where, seen, want]; code 0 = no failure reported.
   std::vector<int64_t> Status();
   std::string StatusString();
@@ -152,6 +156,7 @@ class OverlapImpl : public torch::CustomClassHolder {
   bool nccl_transport_ = false;
   bool engine_ready_ = false;
   at::Tensor phase_trace_;
+  at::Tensor row_trace_;
 };
 
 }  // namespace fo

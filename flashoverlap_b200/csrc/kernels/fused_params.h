@@ -171,6 +171,12 @@ struct alignas(64) FusedParams {
   // [5] rows reduced by this CTA, [6] all rows delivered (CTA 0 of an
   // all-reduce only), [7] unused.
   unsigned long long* phase_trace;
+  // Optional row timeline of the reduce phase, 6 x M x uint64 (null = off), all
+  // by the leading thread of the row group that claimed global row g: [g] row
+  // claimed, [M + g] the row's stores issued, [2M + g] = CTA * 4 + row group,
+  // [3M + g] the partials of all ranks were there, [4M + g] its chunks loaded
+  // and summed, [5M + g] the group passed the row's barrier.
+  unsigned long long* row_trace;
 
   // ---- failure reporting ----------------------------------------------------
   StatusWord* status;

@@ -236,9 +236,9 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   constexpr int BM = 128;
   constexpr int GT = kGroupWarps * 32;  // threads per row
   constexpr int CPT = 8;                // 16-byte chunks per thread held in registers
-  constexpr int NS = NVLS ? 1 : (WS == 0 ? kMaxRanks : WS);
+  constexpr bool GENERIC = !NVLS && WS == 0;  // any number of ranks: sources are added one after the other
+  constexpr int NS = (NVLS || GENERIC) ? 1 : WS;
   constexpr int BATCH = NS >= CPT ? 1 : CPT / NS;  // chunks loaded together
-  constexpr bool PREFETCH = NS == 1;               // next row's loads fit in registers
   const int ws = p.ws;
   const int nsrc = NVLS ? 1 : ws;
   const int n_chunks = p.N >> 3;
@@ -333,6 +333,35 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
       }
     }
   };
+  // generic world size: one chunk summed over all ranks, four loads in flight at a time
+  auto load_sum_generic = [&](const uint16_t* src0, int c) -> uint4 {
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.f;
+    for (int s0 = 0; s0 < ws; s0 += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (s0 + k < ws) v[k] = ptx::ld_cg_v4(src0 + (s0 + k) * src_stride + c * 8);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (s0 + k < ws) {
+          float2 f;
+          f = unpack2<BF16>(v[k].x); a[0] += f.x; a[1] += f.y;
+          f = unpack2<BF16>(v[k].y); a[2] += f.x; a[3] += f.y;
+          f = unpack2<BF16>(v[k].z); a[4] += f.x; a[5] += f.y;
+          f = unpack2<BF16>(v[k].w); a[6] += f.x; a[7] += f.y;
+        }
+      }
+    }
+    uint4 h;
+    h.x = pack2<BF16>(a[0], a[1]);
+    h.y = pack2<BF16>(a[2], a[3]);
+    h.z = pack2<BF16>(a[4], a[5]);
+    h.w = pack2<BF16>(a[6], a[7]);
+    return h;
+  };
   int ready_rb = -1;  // last 128-row block this warp has seen complete (rows are claimed in ascending order)
   // Bounded wait until every rank's partials for block rb have arrived (0 on timeout).
   auto wait_block = [&](int rb) -> uint32_t {
@@ -372,27 +401,57 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   int lr = static_cast<int>(gs->job[0]);
   constexpr uint32_t kDeliveryBatch = 4;
   uint32_t undelivered = 0;  // rows this warp has stored but not yet counted on the delivery counters
-  bool have = false;  // `pre` holds the (summed) chunks of row lr, loaded during the previous iteration
-  uint4 pre[CPT];
+  const bool timeline = p.row_trace != nullptr && leader;
+  constexpr bool PREFETCH = NS == 1 && !GENERIC;  // a second register set for the next row fits
+  bool have = false;  // `pre` holds the chunks of row lr, requested during the previous iteration
+  uint4 pre[PREFETCH ? CPT : 1];
 
   for (int it = 0; lr < rows_local; ++it) {
     const int par = it & 1;
     const int g = global_row(lr);
     const int out_row = p.bcast ? g : lr;
     const uint16_t* src0 = partials_of(lr, g);
+    const unsigned long long t_claim = timeline ? ptx::globaltimer_ns() : 0ull;
     const uint32_t ok = have ? 1u : wait_block(g / BM);
+    const unsigned long long t_ready = timeline ? ptx::globaltimer_ns() : 0ull;
 
     // ---- sum of the partial rows (and the sum of squares) ----
     uint4 h[CPT];
     float ssq = 0.f;
     uint16_t* park = reinterpret_cast<uint16_t*>(p.out[p.me]);  // wide rows only
     if (ok && one_pass) {
-      if (PREFETCH && have) {
+      if constexpr (GENERIC) {
 #pragma unroll
         for (int u = 0; u < CPT; ++u) {
           const int c = u * GT + tid;
           if (c < n_chunks) {
-            h[u] = pre[u];
+            h[u] = load_sum_generic(src0, c);
+            if (p.norm) ssq += sq(h[u]);
+            else store_out(out_row, c, h[u]);
+          }
+        }
+      } else if constexpr (NS == 1) {
+        // One source per chunk: all loads of the row go out back to back.  The
+        // loop holds nothing but the load: an instruction that uses the loaded
+        // value inside the same conditional block is not moved out of it, and
+        // each load would then wait for the one before it.
+        if (have) {
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) h[u] = pre[PREFETCH ? u : 0];
+        } else {
+#pragma unroll
+          for (int u = 0; u < CPT; ++u) {
+            const int c = u * GT + tid;
+            if (c < n_chunks) {
+              if constexpr (NVLS) h[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
+              else h[u] = ptx::ld_cg_v4(src0 + c * 8);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < CPT; ++u) {
+          const int c = u * GT + tid;
+          if (c < n_chunks) {
             if (p.norm) ssq += sq(h[u]);
             else store_out(out_row, c, h[u]);
           }
@@ -435,9 +494,14 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
     } else if (ok) {
       // wide rows: first pass sums and parks the rounded sums in this rank's output row
       for (int c = tid; c < n_chunks; c += GT) {
-        uint4 v[NS];
-        load_chunk(v, src0, c);
-        const uint4 hv = sum_sources(v);
+        uint4 hv;
+        if constexpr (GENERIC) {
+          hv = load_sum_generic(src0, c);
+        } else {
+          uint4 v[NS];
+          load_chunk(v, src0, c);
+          hv = sum_sources(v);
+        }
         if (p.norm) {
           ssq += sq(hv);
           ptx::st_v4(park + layout_offset(p.out_layout, out_row, c * 8), hv);
@@ -446,6 +510,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         }
       }
     }
+    const unsigned long long t_sum = timeline ? ptx::globaltimer_ns() : 0ull;
 
     // ---- one barrier: exchange the partial sums of squares, learn the next row ----
     if (p.norm) {
@@ -462,8 +527,9 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
 #pragma unroll
       for (int w = 0; w < kGroupWarps; ++w) ssq += gs->ssq[par][w];
     }
+    const unsigned long long t_bar = timeline ? ptx::globaltimer_ns() : 0ull;
 
-    // ---- the next row's loads go out before this row is stored, if its partials are there ----
+    // ---- the next row's loads go out before this row is scaled and stored, if its partials are there ----
     have = false;
     if constexpr (PREFETCH) {
       if (one_pass && next_lr < rows_local) {
@@ -471,12 +537,11 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         if (block_ready_now(g2 / BM)) {
           const uint16_t* src2 = partials_of(next_lr, g2);
 #pragma unroll
-          for (int u = 0; u < CPT; ++u) {
+          for (int u = 0; u < CPT; ++u) {  // nothing but the load in this block (see above)
             const int c = u * GT + tid;
             if (c < n_chunks) {
-              uint4 v[NS];
-              load_chunk(v, src2, c);
-              pre[u] = sum_sources(v);
+              if constexpr (NVLS) pre[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src2 + c * 8);
+              else pre[u] = ptx::ld_cg_v4(src2 + c * 8);
             }
           }
           have = true;
@@ -515,6 +580,15 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         if (lane < ws && p.done[lane] != nullptr) ptx::red_release_sys_add(p.done[lane], undelivered);
       }
       undelivered = 0;
+    }
+    if (ok && timeline) {
+      const long long m = p.M;
+      p.row_trace[g] = t_claim;
+      p.row_trace[m + g] = ptx::globaltimer_ns();
+      p.row_trace[2 * m + g] = static_cast<unsigned long long>(blockIdx.x) * 4ull + group;
+      p.row_trace[3 * m + g] = t_ready;
+      p.row_trace[4 * m + g] = t_sum;
+      p.row_trace[5 * m + g] = t_bar;
     }
     if (ok && p.phase_trace != nullptr && leader) {
       t_last = ptx::globaltimer_ns();

@@ -430,11 +430,11 @@ __device__ __forceinline__ void multimem_red_release_add(uint32_t* mc_ptr, uint3
 
 // 16-byte global accesses that bypass L1 (data written by peers or by other
 // SMs of the same kernel must be read at L2, the point of coherence).
-__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
+// 16-byte load that is cached in L2 only (the data was written by another SM or
+// another GPU).  An intrinsic rather than inline assembly: the compiler may
+// then schedule independent loads back to back and their consumers late (it
+// still keeps them behind an acquire, whose asm statement clobbers memory).
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 // Streaming 16-byte store: the data is never read again through this SM's L1,
 // and with nearly all of the SM's memory given to shared memory the little L1
 // that is left must stay available to the stack (register spills).

@@ -164,6 +164,7 @@ void FusedEngine::base_params(FusedParams& p, const SignalArgs* sig) {
   p.l2_hints = l2_hints_ ? 1 : 0;
   p.raster_taper = 0;  // set by the operations that have a reduce phase
   p.phase_trace = phase_trace_;
+  p.row_trace = nullptr;  // set by the operations with a reduce phase when the buffer is large enough
   p.epi_layout.ld = 0;
 }
 
@@ -216,6 +217,7 @@ void FusedEngine::gemm_rmsnorm(const GemmOperands& g_in, void* scratch, void* ou
   if (p.raster_group == 0) p.raster_group = 8;
   p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
+  if (row_trace_ != nullptr && g.M <= row_trace_rows_) p.row_trace = row_trace_;
   p.stage = scratch;
   p.flag_target = static_cast<uint32_t>(g.N / tc.bn);
   p.norm = norm.gamma != nullptr;
@@ -268,6 +270,7 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
   p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
+  if (row_trace_ != nullptr && g.M <= row_trace_rows_) p.row_trace = row_trace_;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
   p.norm = norm.gamma != nullptr;
@@ -334,6 +337,7 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
   p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
+  if (row_trace_ != nullptr && g.M <= row_trace_rows_) p.row_trace = row_trace_;
   p.stage = heap_.local(ws_.stage[set]);
   p.flag_target = static_cast<uint32_t>(world_ * (g.N / tc.bn));
   p.norm = norm.gamma != nullptr;

@@ -65,6 +65,13 @@ class FusedEngine {
   // Device buffer of kTraceWords x uint64 per CTA that every following launch
   // fills with its phase timestamps (null = off).
   void set_phase_trace(unsigned long long* buf) { phase_trace_ = buf; }
+  // Device buffer of `rows` x 6 x uint64: the reduce phase of every following
+  // launch of at most `rows` rows records, per global row, when it was claimed,
+  // ready, summed, past its barrier and stored, and which CTA and row group did it (null = off).
+  void set_row_trace(unsigned long long* buf, long long rows) {
+    row_trace_ = buf;
+    row_trace_rows_ = buf != nullptr ? rows : 0;
+  }
 
   // C[M,N] = A[M,K] * B[N,K]^T on this GPU only.  `layout` null = row-major.
   void gemm(const GemmOperands& g, void* C, const OutLayout* layout, const SignalArgs* sig, cudaStream_t stream);
@@ -211,6 +218,8 @@ class FusedEngine {
   // them, which is what lets the GEMM overlap the transfer: multicast is an option, not the default.
   bool nvls_ag_ = false;
   unsigned long long* phase_trace_ = nullptr;
+  unsigned long long* row_trace_ = nullptr;
+  long long row_trace_rows_ = 0;
   unsigned long long calls_ = 0;  // fused collective calls issued so far
   void* ag_dst_scratch_[kMaxRanks] = {};  // destination of this rank's block on every rank (per call)
   unsigned long long pushes_ = 0;  // arrivals expected at the push counter so far

@@ -105,6 +105,37 @@ def test_phase_trace_records_every_row_once():
     assert bool((t[:, 1] >= t[:, 0]).all())   # GEMM phase ends after the start
 
 
+def test_row_trace_has_ordered_stamps_for_every_row():
+    M, N, K = 1024, 2048, 256
+    A, B, W = make_inputs(M, N, K, torch.float16, seed=5)
+    C = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    O = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    impl = make_impl()
+    rows = torch.zeros(6 * M, dtype=torch.int64, device="cuda")
+    impl.set_row_trace(rows)
+    impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, 0)
+    torch.cuda.synchronize()
+    impl.set_row_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
+    impl.check_status()
+    r = rows.view(6, M).cpu()
+    claimed, stored, who, ready, summed, barrier = r[0], r[1], r[2], r[3], r[4], r[5]
+    assert bool((claimed > 0).all())                       # every row was reduced by somebody
+    assert bool((claimed <= ready).all() and (ready <= summed).all() and (summed <= barrier).all()
+                and (barrier <= stored).all())
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert int(who.max()) < 4 * sms and int((who % 4).max()) <= 2   # CTA * 4 + row group (0..2)
+    want = rms_ref(A.float() @ B.float().t(), W, 1e-5)
+    assert (O.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item()
+    with pytest.raises(RuntimeError):
+        impl.set_row_trace(torch.zeros(7, dtype=torch.int64, device="cuda"))  # not a multiple of 6
+    # a buffer that is too small for the next call is ignored rather than overrun
+    impl.set_row_trace(torch.zeros(6 * 128, dtype=torch.int64, device="cuda"))
+    impl.gemm_rmsnorm(A, B, C, O, W, 1e-5, 0)
+    torch.cuda.synchronize()
+    impl.set_row_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
+    impl.check_status()
+
+
 @pytest.mark.parametrize("with_norm", [False, True])
 def test_world1_allreduce_and_reducescatter(with_norm):
     M, N, K = 512, 2048, 256

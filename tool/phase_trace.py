@@ -110,13 +110,16 @@ def main():
         ts = time_steps(fused, 10, 3)
         tg = time_steps(lambda: impl.cutlass_gemm(A, B, C, args.algo), 10, 3)
         trace = torch.zeros(8 * sms, dtype=torch.int64, device="cuda")
+        rows_t = torch.zeros(6 * M, dtype=torch.int64, device="cuda")
         impl.set_phase_trace(trace)
+        impl.set_row_trace(rows_t)
         flush_l2()
         if ws > 1:
             dist.barrier()
         fused()
         torch.cuda.synchronize()
         impl.set_phase_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
+        impl.set_row_trace(torch.empty(0, dtype=torch.int64, device="cuda"))
         impl.check_status()
         t = trace.view(sms, 8).cpu().double()
         t0 = t[:, 0].min()
@@ -125,9 +128,20 @@ def main():
         first = ((t[used, 4] - t0) / 1e3).min().item() if used.any() else float("nan")
         last = ((t[:, 2] - t0) / 1e3).max().item()
         delivered = (t[0, 6] - t0).item() / 1e3 if t[0, 6] > 0 else float("nan")
+        # row timeline of the reduce phase (rows this rank owns): stages of one row, and how many rows were
+        # already stored when the last CTA left the GEMM phase
+        R = rows_t.view(6, M).cpu().double()
+        mine = R[1] > 0
+        stage_us = [float("nan")] * 4
+        done_early = 0.0
+        if mine.any():
+            claim, end, ready, summed, bar = R[0][mine], R[1][mine], R[3][mine], R[4][mine], R[5][mine]
+            stage_us = [((ready - claim) / 1e3).median().item(), ((summed - ready) / 1e3).median().item(),
+                        ((bar - summed) / 1e3).median().item(), ((end - bar) / 1e3).median().item()]
+            done_early = ((end - t0) / 1e3 <= ge.max()).double().mean().item()
         row = torch.tensor([sorted(ts)[len(ts) // 2] * 1e3, sorted(tg)[len(tg) // 2] * 1e3, ge.min().item(),
-                            ge.median().item(), ge.max().item(), first, last, delivered], dtype=torch.float64,
-                           device="cuda")
+                            ge.median().item(), ge.max().item(), first, last, delivered, *stage_us, done_early],
+                           dtype=torch.float64, device="cuda")
         rows = [torch.zeros_like(row) for _ in range(ws)]
         if ws > 1:
             dist.all_gather(rows, row)
@@ -142,6 +156,13 @@ def main():
                 v = v.tolist()
                 lines.append(f"| {r} | {v[0]:.0f} | {v[1]:.0f} | {v[2]:.0f} / {v[3]:.0f} / {v[4]:.0f} | {v[5]:.0f} | "
                              f"{v[6]:.0f} | {v[7]:.0f} |")
+            lines.append("\nOne row in its row group (median, us): wait for the partials / load and sum / barrier / scale "
+                         "and store; share of the rank's rows stored before the last CTA left the GEMM phase:\n")
+            lines.append("| rank | wait | load + sum | barrier | scale + store | rows stored during the GEMM phase |\n"
+                         "|---|---|---|---|---|---|")
+            for r, v in enumerate(rows):
+                v = v.tolist()
+                lines.append(f"| {r} | {v[8]:.2f} | {v[9]:.2f} | {v[10]:.2f} | {v[11]:.2f} | {100 * v[12]:.0f} % |")
     lines += gather_trace(impl, rank, ws, sms, args)
     if rank == 0:
         text = "\n".join(lines) + "\n"
