@@ -243,6 +243,7 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
   const int nsrc = NVLS ? 1 : ws;
   const int n_chunks = p.N >> 3;
   const bool one_pass = n_chunks <= GT * CPT;
+  const int last_chunk = n_chunks - 1;
   const int tid = wg * 32 + lane;
   const int rows_local = p.rows_per_owner;
   const uint16_t* stage = reinterpret_cast<const uint16_t*>(p.stage);
@@ -278,14 +279,12 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
 #pragma unroll
       for (int e = 0; e < 8; ++e) a[e] = 0.f;
 #pragma unroll
-      for (int sidx = 0; sidx < NS; ++sidx) {
-        if (sidx < nsrc) {
-          float2 f;
-          f = unpack2<BF16>(v[sidx].x); a[0] += f.x; a[1] += f.y;
-          f = unpack2<BF16>(v[sidx].y); a[2] += f.x; a[3] += f.y;
-          f = unpack2<BF16>(v[sidx].z); a[4] += f.x; a[5] += f.y;
-          f = unpack2<BF16>(v[sidx].w); a[6] += f.x; a[7] += f.y;
-        }
+      for (int sidx = 0; sidx < NS; ++sidx) {  // NS is the number of ranks here
+        float2 f;
+        f = unpack2<BF16>(v[sidx].x); a[0] += f.x; a[1] += f.y;
+        f = unpack2<BF16>(v[sidx].y); a[2] += f.x; a[3] += f.y;
+        f = unpack2<BF16>(v[sidx].z); a[4] += f.x; a[5] += f.y;
+        f = unpack2<BF16>(v[sidx].w); a[6] += f.x; a[7] += f.y;
       }
       uint4 h;
       h.x = pack2<BF16>(a[0], a[1]);
@@ -431,63 +430,54 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
           }
         }
       } else if constexpr (NS == 1) {
-        // One source per chunk: all loads of the row go out back to back.  The
-        // loop holds nothing but the load: an instruction that uses the loaded
-        // value inside the same conditional block is not moved out of it, and
-        // each load would then wait for the one before it.
+        // One source per chunk: all loads of the row go out back to back.  They
+        // are unconditional (a chunk index past the end of the row is clamped,
+        // the value ignored): a load inside a conditional block together with
+        // an instruction that uses its value waits for the load before it.
         if (have) {
 #pragma unroll
           for (int u = 0; u < CPT; ++u) h[u] = pre[PREFETCH ? u : 0];
         } else {
 #pragma unroll
           for (int u = 0; u < CPT; ++u) {
-            const int c = u * GT + tid;
-            if (c < n_chunks) {
-              if constexpr (NVLS) h[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
-              else h[u] = ptx::ld_cg_v4(src0 + c * 8);
-            }
+            const int c = min(u * GT + tid, last_chunk);
+            if constexpr (NVLS) h[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src0 + c * 8);
+            else h[u] = ptx::ld_cg_v4(src0 + c * 8);
           }
         }
 #pragma unroll
         for (int u = 0; u < CPT; ++u) {
           const int c = u * GT + tid;
-          if (c < n_chunks) {
-            if (p.norm) ssq += sq(h[u]);
-            else store_out(out_row, c, h[u]);
-          }
+          if (p.norm) ssq += c < n_chunks ? sq(h[u]) : 0.f;
+          else if (c < n_chunks) store_out(out_row, c, h[u]);
         }
       } else {
-        // software pipeline: the loads of batch k+1 are in flight while batch k is summed
-        uint4 cur[BATCH][NS], nxt[BATCH][NS];
-#pragma unroll
-        for (int u = 0; u < BATCH; ++u) {
-          const int c = u * GT + tid;
-          if (c < n_chunks) load_chunk(cur[u], src0, c);
-        }
-#pragma unroll
-        for (int b0 = 0; b0 < CPT; b0 += BATCH) {
-          if (b0 + BATCH < CPT) {
-#pragma unroll
-            for (int u = 0; u < BATCH; ++u) {
-              const int c = (b0 + BATCH + u) * GT + tid;
-              if (c < n_chunks) load_chunk(nxt[u], src0, c);
-            }
-          }
+        // Software pipeline over batches of chunks: the loads of batch k+1 are in
+        // flight while batch k is summed.  Two register sets alternate by the
+        // (compile-time) batch index, so nothing is copied; the loads are
+        // unconditional (a chunk index past the row's end is clamped and its
+        // value ignored), so that they form straight-line code and all go out
+        // before the first use.
+        constexpr int NB = CPT / BATCH;
+        uint4 buf[2][BATCH][NS];
+        auto issue = [&](int k, uint4 (&dst)[BATCH][NS]) {
 #pragma unroll
           for (int u = 0; u < BATCH; ++u) {
-            const int c = (b0 + u) * GT + tid;
-            if (c < n_chunks) {
-              h[b0 + u] = sum_sources(cur[u]);
-              if (p.norm) ssq += sq(h[b0 + u]);
-              else store_out(out_row, c, h[b0 + u]);
-            }
+            const int c = min((k * BATCH + u) * GT + tid, last_chunk);
+#pragma unroll
+            for (int sidx = 0; sidx < NS; ++sidx) dst[u][sidx] = ptx::ld_cg_v4(src0 + sidx * src_stride + c * 8);
           }
-          if (b0 + BATCH < CPT) {
+        };
+        issue(0, buf[0]);
 #pragma unroll
-            for (int u = 0; u < BATCH; ++u) {
+        for (int k = 0; k < NB; ++k) {
+          if (k + 1 < NB) issue(k + 1, buf[(k + 1) & 1]);
 #pragma unroll
-              for (int sidx = 0; sidx < NS; ++sidx) cur[u][sidx] = nxt[u][sidx];
-            }
+          for (int u = 0; u < BATCH; ++u) {
+            const int c = (k * BATCH + u) * GT + tid;
+            h[k * BATCH + u] = sum_sources(buf[k & 1][u]);
+            if (p.norm) ssq += c < n_chunks ? sq(h[k * BATCH + u]) : 0.f;
+            else if (c < n_chunks) store_out(out_row, c, h[k * BATCH + u]);
           }
         }
       }
@@ -537,12 +527,10 @@ __device__ __forceinline__ void comm_worker(const FusedParams& p, GroupScratch* 
         if (block_ready_now(g2 / BM)) {
           const uint16_t* src2 = partials_of(next_lr, g2);
 #pragma unroll
-          for (int u = 0; u < CPT; ++u) {  // nothing but the load in this block (see above)
-            const int c = u * GT + tid;
-            if (c < n_chunks) {
-              if constexpr (NVLS) pre[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src2 + c * 8);
-              else pre[u] = ptx::ld_cg_v4(src2 + c * 8);
-            }
+          for (int u = 0; u < CPT; ++u) {
+            const int c = min(u * GT + tid, last_chunk);
+            if constexpr (NVLS) pre[u] = ptx::multimem_ld_reduce_add_v4<BF16>(src2 + c * 8);
+            else pre[u] = ptx::ld_cg_v4(src2 + c * 8);
           }
           have = true;
         }

@@ -175,41 +175,80 @@ def hint_from_samples(samples: torch.Tensor, wave_size: int, min_agree: int = 0)
     return ok, hint
 
 
+def raster_group_sizes(tile_rows: int, raster_group: int, taper: bool = True) -> List[int]:
+    """Tile rows per raster group in the order the kernel walks them: full
+    groups, and with ``taper`` the last ones shrink by halves down to 1, 1 (the
+    same rule as ``tile_coords`` in the kernel)."""
+    G = max(int(raster_group), 1)
+    remaining, size, out = int(tile_rows), G, []
+    if not taper:
+        while remaining > 0:
+            out.append(min(G, remaining))
+            remaining -= out[-1]
+        return out
+    while remaining > 0:
+        if remaining <= size:
+            size = (remaining + 1) // 2 if remaining > 1 else 1
+        out.append(size)
+        remaining -= size
+    return out
+
+
 def predict_fused_ms(M: int, N: int, gemm_ms: float, world_size: int, comm_op: str, link_gbs: float,
                      transport: str = "p2p", hbm_gbs: float = 6500.0, elem_bytes: int = 2, tile_m: int = 256,
-                     raster_group: int = 2, sm_count: int = 148, latency_us: float = 8.0) -> float:
-    """Cost model of this library's fused kernel: one launch in which the
-    communication warps reduce and deliver finished rows while the tensor cores
+                     raster_group: int = 2, sm_count: int = 148, latency_us: float = 8.0, taper: bool = True,
+                     row_us: float = 0.0, groups_gemm: int = 1, groups_tail: int = 3) -> float:
+    """Cost model of this library's fused kernel: one launch in which row
+    groups (4 warps) reduce and deliver finished rows while the tensor cores
     compute later tiles.
 
-    * The GEMM and the collective overlap, so the body costs the slower of the
-      two: ``gemm_ms`` against the bytes one GPU must move per NVLink direction
-      at ``link_gbs`` (the MEASURED bandwidth of the transport, from the curve
-      files).  Bytes per direction, with S = M*N*elem_bytes and n ranks:
-      all-reduce over peer-to-peer stores 2*S*(n-1)/n (partials out, results
-      out), all-reduce over NVLink SHARP S*(1+1/n) (the switch pulls every
-      partial once and multicasts every result once), reduce-scatter S*(n-1)/n
-      (or S over NVLink SHARP).
-    * What cannot overlap is the tail: the rows of the last ``raster_group`` tile
-      rows can only be reduced once the GEMM has ended.  Their bytes go over the
-      link after the last tile, plus one round-trip latency.
-    * With one rank the "link" is HBM: the rows are read and written once.
+    The rows of a raster group can be reduced once the whole group is computed.
+    The model walks the groups in the kernel's order: group j completes at
+    ``gemm_ms`` times its share of the tiles and adds its rows (this rank's
+    1/n of them) to a queue; the queue drains at ``groups_gemm`` row groups per
+    SM while the GEMM runs and ``groups_tail`` per SM after it, each taking
+    ``row_us`` per row (MEASURED by ``tune.runtime.measure_row_us``: it holds
+    the memory, link and latency cost of one row on this machine).  What is
+    left in the queue when the last tile is done is the tail.  Without a
+    measured ``row_us`` the row time is taken from the bytes of one row at the
+    link (or, with one rank, HBM) bandwidth.
+
+    The result is never below the time the collective's bytes need at
+    ``link_gbs``, the MEASURED bandwidth of the transport.  Bytes per NVLink
+    direction, with S = M*N*elem_bytes and n ranks: all-reduce over
+    peer-to-peer stores 2*S*(n-1)/n, over NVLink SHARP S*(1+1/n);
+    reduce-scatter S*(n-1)/n (S over NVLink SHARP); one rank: HBM, 2*S.
     """
     n = max(world_size, 1)
     S = float(M) * N * elem_bytes
     if n == 1:
-        per_dir = 2.0 * S
-        bw = hbm_gbs
+        per_dir, bw = 2.0 * S, hbm_gbs
     elif comm_op == "all_reduce":
         per_dir = S * (1.0 + 1.0 / n) if transport == "nvls" else 2.0 * S * (n - 1) / n
         bw = link_gbs
     else:
         per_dir = S if transport == "nvls" else S * (n - 1) / n
         bw = link_gbs
-    comm_ms = per_dir / (bw * 1e9) * 1e3
-    tail_rows = min(M, tile_m * max(raster_group, 1))
-    tail_ms = comm_ms * tail_rows / M + latency_us * 1e-3
-    return max(gemm_ms, comm_ms * (1.0 - tail_rows / M)) + tail_ms
+    comm_us = per_dir / (bw * 1e9) * 1e6
+    rows_owned = M / n
+    if row_us <= 0.0:
+        # all row groups of the GPU together move the collective's bytes at the measured bandwidth
+        row_us = comm_us / max(rows_owned, 1.0) * sm_count * groups_tail
+    gemm_us = gemm_ms * 1e3
+    sizes = raster_group_sizes(div_up(M, tile_m), raster_group, taper)
+    total = float(sum(sizes))
+    rate_gemm = sm_count * groups_gemm / row_us   # rows per us while the GEMM runs
+    rate_tail = sm_count * groups_tail / row_us
+    t_prev, backlog, done = 0.0, 0.0, 0.0
+    for size in sizes:
+        done += size
+        t = gemm_us * done / total
+        backlog = max(0.0, backlog - rate_gemm * (t - t_prev))
+        backlog += size * tile_m / n
+        t_prev = t
+    end_us = gemm_us + backlog / rate_tail + latency_us
+    first_us = gemm_us * sizes[0] / total
+    return max(end_us, first_us + comm_us * (1.0 - 1.0 / len(sizes)) + latency_us, comm_us + latency_us) * 1e-3
 
 
 def _algo_tiles():

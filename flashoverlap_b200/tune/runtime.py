@@ -276,3 +276,28 @@ def pick_algo_by_timing(run: Callable[[int], None], algos: Sequence[int], warmup
         timed.append((a, mean_time_ms(lambda: run(a), warmup, reps, flush=True)))
     best = min(timed, key=lambda t: t[1])[0]
     return best, timed
+
+
+def measure_row_us(impl, N: int, comm_op: str, dtype=torch.float16, algo: int = 0, M: int = 4096, K: int = 64,
+                   warmup: int = 3, reps: int = 10, sms: int = 148, groups: int = 3) -> float:
+    """Time one row group needs for one row of ``N`` values in the reduce phase
+    of ``comm_op`` on this machine, in us: a GEMM with a negligible K leaves the
+    fused kernel's time to its reduce phase, in which every SM runs ``groups``
+    row groups: (fused - GEMM alone) * groups * SMs / rows per rank.  It is the
+    one number the fused cost model needs besides the GEMM time and the link
+    bandwidth (memory, link and latency cost of a row, measured rather than
+    assumed)."""
+    _, ws = world()
+    while M % ws or (M // ws) % 128:
+        M *= 2
+    A, B, C = make_inputs(M, N, K, dtype)
+    W = torch.ones(N, device="cuda", dtype=dtype)
+    D = torch.empty(M // ws, N, device="cuda", dtype=dtype)
+    if comm_op == "all_reduce":
+        fused = lambda: impl.gemm_allreduce_fused(A, B, W, 1e-5, algo)  # noqa: E731
+    else:
+        fused = lambda: impl.gemm_reducescatter_fused(A, B, D, W, 1e-5, algo, False)  # noqa: E731
+    t_fused = mean_time_ms(fused, warmup, reps, flush=True)
+    t_gemm = mean_time_ms(lambda: impl.cutlass_gemm(A, B, C, algo), warmup, reps, flush=True)
+    rows = M // ws
+    return max((t_fused - t_gemm) * 1e3, 1.0) * groups * sms / rows

@@ -27,7 +27,7 @@ import torch
 
 from ..utils import config as cfg
 from .model import best_segmentation, div_up, predict_fused_ms
-from .runtime import compute_hint, dbg, perf_running, search_two_stream, world
+from .runtime import compute_hint, dbg, measure_row_us, perf_running, search_two_stream, world
 
 RASTER_CHOICES = (1, 2, 4, 8)
 
@@ -120,11 +120,13 @@ def link_bandwidth_from_curves(world_size: int, multinode: bool = False, path=No
 
 def predictive_search(impl, M: int, N: int, K: int, comm_op: str, curve: torch.Tensor,
                       link_gbs: Optional[float] = None, dtype=torch.float16, path=None, top_k: int = 3,
-                      reps: int = 50, verbose: bool = True, link_kind: str = "p2p", seg_reps: int = 20) -> dict:
+                      reps: int = 50, verbose: bool = True, link_kind: str = "p2p", seg_reps: int = 20,
+                      row_us: Optional[float] = None) -> dict:
     """Ranks candidates with the cost models on measured bandwidth, then times
     only the best few.  ``curve`` is the measured NCCL curve of ``comm_op``
     (for the two-stream grouping), ``link_gbs`` the measured bandwidth of the
-    fused kernel's transport (``link_kind``: "p2p" or "nvls")."""
+    fused kernel's transport (``link_kind``: "p2p" or "nvls"), ``row_us`` the
+    measured time of one row in the reduce phase (measured here if not given)."""
     rank, ws = world()
     if link_gbs is None:
         if ws > 1:
@@ -134,12 +136,16 @@ def predictive_search(impl, M: int, N: int, K: int, comm_op: str, curve: torch.T
     data = cfg.load_config(M, N, K, path)
     BM_l, BN_l, dur_l, Algo_l = cfg.stage1_lists(data)
     by_raster = cfg.stage1_raster_table(data)  # GEMM time per (configuration, raster group), if profiled
+    if row_us is None:
+        row_us = measure_row_us(impl, N, comm_op, dtype, algo=Algo_l[0])  # what one row costs a row group here
+    if rank == 0 and verbose:
+        print(f"Measured row time of the reduce phase: {row_us:.2f} us per row group.")
     ranked = []
     for t in range(min(10, len(BM_l))):
         for rg in knob_candidates(M, BM_l[t]):
             gemm_ms = by_raster[rg][t] if rg in by_raster else dur_l[t]
             est = predict_fused_ms(M, N, gemm_ms, ws, comm_op, link_gbs, transport=link_kind, tile_m=BM_l[t],
-                                   raster_group=rg)
+                                   raster_group=rg, row_us=row_us, sm_count=sm_count())
             ranked.append((est, t, rg))
     ranked.sort()
     best = None

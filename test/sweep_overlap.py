@@ -11,7 +11,8 @@ For every shape and both collectives the script
    group) candidate and keeps the best,
 3. predictive: ranks the same candidates with the cost model on the GEMM times
    of step 1 and the link bandwidth MEASURED at the start of the run (the
-   library's own transport, 64 MiB messages) and times only the model's first
+   library's own transport, 64 MiB messages) and the time one row costs a row
+   group (measured with a GEMM of negligible K), and times only the model's first
    pick; when the picks differ both are timed again in alternation and the gap
    is the ratio of those times,
 4. times the non-overlapped baseline (cuBLAS GEMM, one NCCL collective, RMSNorm
@@ -33,7 +34,7 @@ import torch  # noqa: E402
 from flashoverlap_b200.cli import DTYPES, finish, make_baseline_impl, make_overlap_impl, start  # noqa: E402
 from flashoverlap_b200.parallel import max_over_ranks  # noqa: E402
 from flashoverlap_b200.tune.model import predict_fused_ms  # noqa: E402
-from flashoverlap_b200.tune.runtime import mean_time_ms  # noqa: E402
+from flashoverlap_b200.tune.runtime import mean_time_ms, measure_row_us  # noqa: E402
 from flashoverlap_b200.tune.search import knob_candidates  # noqa: E402
 from flashoverlap_b200.utils.config import ALGO_TILES  # noqa: E402
 from flashoverlap_b200.utils.timing import time_pairs  # noqa: E402
@@ -69,9 +70,13 @@ def main():
     impl = make_overlap_impl(max_m=max(args.m_list), max_n=max(args.n_list))
     base = make_baseline_impl()
     link_gbs, link_kind = measure_link(impl, ws)
+    # what one row of N values costs a row group in the reduce phase (measured once per N and collective)
+    row_us = {(op, N): measure_row_us(impl, N, op, dt, algo=args.algos[0]) for op in ("all_reduce", "reduce_scatter")
+              for N in args.n_list}
     rows_md = []
     if rank == 0:
-        print(f"TP={ws} {args.dtype}; measured link {link_gbs:.0f} GB/s per direction ({link_kind})")
+        print(f"TP={ws} {args.dtype}; measured link {link_gbs:.0f} GB/s per direction ({link_kind}); row time "
+              + ", ".join(f"{op} N={n}: {v:.1f} us" for (op, n), v in row_us.items()))
         print(f"{'op':>3} {'M':>6} {'N':>6} {'K/rank':>7} | {'exh ms':>8} {'pick':>10} | {'pred ms':>8} {'pick':>10} "
               f"{'gap':>6} | {'base ms':>8} {'x':>5}")
     agree = total = 0
@@ -117,7 +122,8 @@ def main():
                     ex = min(times, key=times.get)
                     kind = link_kind if op == "all_reduce" else "p2p"
                     pred = {c: predict_fused_ms(M, N, gemm_ms[c], ws, op, link_gbs, transport=kind,
-                                                tile_m=ALGO_TILES[c[0]][0], raster_group=c[1]) for c in cands}
+                                                tile_m=ALGO_TILES[c[0]][0], raster_group=c[1], row_us=row_us[(op, N)])
+                            for c in cands}
                     pr = min(pred, key=pred.get)
                     pr_ms = timed(*pr)                                          # predictive: only its pick is timed
                     if pr == ex:

@@ -152,3 +152,30 @@ def test_fused_cost_model_orders_regimes():
     # a compute-bound problem costs its GEMM plus a tail that grows with the raster group
     big = model.predict_fused_ms(8192, 8192, 0.30, 8, "reduce_scatter", 550.0, raster_group=1)
     assert 0.30 < big < model.predict_fused_ms(8192, 8192, 0.30, 8, "reduce_scatter", 550.0, raster_group=8)
+
+
+def test_raster_group_sizes_follow_the_kernels_taper():
+    assert model.raster_group_sizes(16, 8) == [8, 4, 2, 1, 1]
+    assert model.raster_group_sizes(16, 4) == [4, 4, 4, 2, 1, 1]
+    assert model.raster_group_sizes(16, 8, taper=False) == [8, 8]
+    assert model.raster_group_sizes(5, 2) == [2, 2, 1]          # 5 -> 2, 3 -> 2, 1 -> 1
+    assert model.raster_group_sizes(1, 8) == [1]
+    for tm in range(1, 40):
+        for g in (1, 2, 4, 8, 16):
+            assert sum(model.raster_group_sizes(tm, g)) == tm
+            assert sum(model.raster_group_sizes(tm, g, taper=False)) == tm
+
+
+def test_fused_model_queues_rows_behind_slow_row_groups():
+    # fast rows: the reduce phase hides under the GEMM, the raster group hardly matters
+    fast = [model.predict_fused_ms(4096, 8192, 0.36, 1, "all_reduce", 1.0, raster_group=g, row_us=1.0) for g in (1, 8)]
+    assert abs(fast[0] - fast[1]) < 0.01 and 0.36 < fast[0] < 0.40
+    # slow rows: a large first group leaves a backlog at the end of the GEMM
+    slow = [model.predict_fused_ms(4096, 8192, 0.36, 1, "all_reduce", 1.0, raster_group=g, row_us=30.0) for g in (1, 8)]
+    assert slow[1] >= slow[0] > fast[0]
+    # never below the time the bytes need on the link
+    assert model.predict_fused_ms(4096, 8192, 0.01, 8, "all_reduce", 400.0, transport="nvls", row_us=1.0) >= \
+        4096 * 8192 * 2 * 1.125 / 400e9 * 1e3
+    # without the taper the last group's rows wait for the last tile
+    assert model.predict_fused_ms(4096, 8192, 0.17, 2, "all_reduce", 500.0, raster_group=8, row_us=10.0, taper=False) > \
+        model.predict_fused_ms(4096, 8192, 0.17, 2, "all_reduce", 500.0, raster_group=8, row_us=10.0, taper=True)

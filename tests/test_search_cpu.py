@@ -39,6 +39,7 @@ def patched(monkeypatch, tmp_path):
     monkeypatch.setattr(torch.cuda, "get_device_properties", lambda *a, **k: types.SimpleNamespace(multi_processor_count=148))
     monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
     monkeypatch.setattr(search, "compute_hint", compute_hint)
+    monkeypatch.setattr(search, "measure_row_us", lambda *a, **k: 6.0)
     monkeypatch.setattr(search, "sm_count", lambda: 148)
     monkeypatch.setattr(search, "world", lambda: (0, 8))
     monkeypatch.setattr(cfg, "gpu_tag", lambda name=None: "b200")
