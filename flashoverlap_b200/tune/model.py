@@ -265,9 +265,11 @@ def gather_algo_candidates(rows_per_source: int, n: int, sms: int = 148) -> List
     quarter of the machine busy per step) but 80 tiles of 128 x 128.  Returns
     the configurations ordered by the estimated time per block, best first:
     waves needed for the block's tiles times the area of a tile, with small
-    tiles charged for their lower tensor-core efficiency."""
+    tiles charged for their measured lower throughput."""
     rows = max(int(rows_per_source), 1)
-    penalty = {256 * 256: 1.0, 256 * 128: 1.08, 128 * 256: 1.08, 128 * 128: 1.2, 256 * 64: 1.3, 128 * 64: 1.5}
+    # time per output element relative to the 256 x 256 CTA-pair tile, from the stage-1 profile of a
+    # 4096 x 8192 x 4096 GEMM (tune/profile_config.py) on a B200
+    penalty = {(256, 256): 1.0, (128, 256): 1.13, (128, 128): 1.34, (256, 128): 1.6, (128, 64): 2.3, (256, 64): 2.8}
     scored = []
     for algo, (bm, bn, bk) in enumerate(_algo_tiles()):
         if bk != 128 and (bm, bn) != (128, 256):   # one K depth per tile shape
@@ -278,7 +280,7 @@ def gather_algo_candidates(rows_per_source: int, n: int, sms: int = 148) -> List
         tiles = -(-rows // bm) * (n // bn)
         slots = max(1, sms // ctas)
         waves = -(-tiles // slots)
-        per_tile = bm * bn / ctas * penalty.get(bm * bn, 1.5)
+        per_tile = bm * bn / ctas * penalty.get((bm, bn), 2.0)
         scored.append((waves * per_tile, -bm * bn, algo))
     scored.sort()
     return [a for _, _, a in scored]

@@ -41,31 +41,35 @@ class ClockSampler:
         self._proc: Optional[subprocess.Popen] = None
         self._path: Optional[str] = None
         self._nvml = None
+        self._handle = None
+        self._max_sm = 0.0
 
     # ---- NVML thread -----------------------------------------------------
-    def _run(self):
-        nv = self._nvml
+    def _sample(self):
+        nv, h = self._nvml, self._handle
         try:
-            h = nv.nvmlDeviceGetHandleByIndex(self.gpu_index)
-            max_sm = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+            power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+            reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+            self._samples.append((sm, self._max_sm, power, reasons))
         except Exception:
-            return
+            pass
+
+    def _run(self):
         while not self._stop.is_set():
-            try:
-                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                power = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
-                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                self._samples.append((sm, max_sm, power, reasons))
-            except Exception:
-                pass
+            self._sample()
             time.sleep(self.period_ms / 1000.0)
 
     def __enter__(self):
         try:
             import pynvml
 
+            # library and device handle are set up before the sampled region starts: a short region
+            # (a few tens of milliseconds) would otherwise be over before the first sample
             pynvml.nvmlInit()
             self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self._max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
             return self
@@ -90,6 +94,7 @@ class ClockSampler:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=2)
+            self._sample()  # one more right at the end of the region: the GPU has not yet clocked down
         if self._proc is not None:
             self._proc.send_signal(signal.SIGINT)
             try:

@@ -91,3 +91,30 @@ def test_two_stream_search_predictive_times_only_its_picks(fake_gpu):
 def test_reduce_scatter_candidates_keep_rank_blocks_whole(fake_gpu):
     _, _, timed = runtime.search_two_stream(None, 4096, 8192, 1024, 3, "reduce_scatter", max_units=4)
     assert all((x * 256) % 8 == 0 for g, _ in timed for x in g)
+
+
+def test_clock_sampler_with_a_fake_nvml(monkeypatch):
+    """The sampler reads clocks, power and throttle reasons through NVML and never sets anything; a region
+    that is over before the polling thread wakes up still gets the sample taken at its end."""
+    import sys
+    import types
+
+    calls = []
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: calls.append("init")
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("handle", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, k: 1965
+    fake.nvmlDeviceGetClockInfo = lambda h, k: 1400
+    fake.nvmlDeviceGetPowerUsage = lambda h: 950_000
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    from flashoverlap_b200.utils.clocks import ClockSampler
+
+    with ClockSampler(0, period_ms=1000.0) as s:
+        pass  # an empty region
+    out = s.summary()
+    assert out["samples"] >= 1 and out["sm_mhz"] == 1400 and out["sm_max_mhz"] == 1965
+    assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 950.0
+    assert not any(name.startswith("nvmlDeviceSet") for name in dir(fake))

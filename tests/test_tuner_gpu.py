@@ -59,3 +59,21 @@ def test_profile_hint_search_and_use(tmp_path):
     ref = ref * torch.rsqrt(ref.pow(2).mean(-1, keepdim=True) + 1e-5)
     assert (y.float() - ref).abs().max().item() < 2e-2
     impl.check_status()
+
+
+def test_measured_row_time_is_sane():
+    from flashoverlap_b200.tune.runtime import gather_algo_candidates, measure_row_us, pick_algo_by_timing
+
+    impl = make_overlap_impl(timeout_ms=3000)
+    row_ar = measure_row_us(impl, 2048, "all_reduce", torch.float16, reps=3)
+    row_rs = measure_row_us(impl, 2048, "reduce_scatter", torch.bfloat16, reps=3)
+    assert 0.05 < row_ar < 200.0 and 0.05 < row_rs < 200.0   # microseconds per row and row group
+    impl.check_status()
+    # the timed tile pick returns one of its candidates and a time for each
+    A = torch.randn(1024, 256, device="cuda", dtype=torch.float16)
+    B = torch.randn(2048, 256, device="cuda", dtype=torch.float16)
+    C = torch.empty(1024, 2048, device="cuda", dtype=torch.float16)
+    cands = gather_algo_candidates(1024, 2048)[:3]
+    best, timed = pick_algo_by_timing(lambda a: impl.allgather_gemm(A, B, C, a), cands, warmup=1, reps=2)
+    assert best in cands and [a for a, _ in timed] == cands and all(t > 0 for _, t in timed)
+    impl.check_status()
