@@ -132,8 +132,20 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     O2 = torch.empty_like(D2)
     F2 = torch.empty_like(D2)
 
+    # raster group (tile rows walked together) of this shape, searched like the tuner's stage 2: timed candidates
+    rs_raster, rs_timed = 0, []
+    if world > 1:
+        def run_raster(rg):
+            impl.set_raster_group(rg)
+            impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, algo, False)
+
+        rs_raster, rs_timed = pick_algo_by_timing(run_raster, [2, 4, 8], warmup=1, reps=3)
+        impl.set_raster_group(0)
+
     def fused_rs():
+        impl.set_raster_group(rs_raster)
         impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, algo, False)
+        impl.set_raster_group(0)
 
     def base_rs():
         base.gemm_reducescatter(A2, B2, C2, D2)
@@ -147,6 +159,8 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
         "speedup_vs_nccl_baseline": round(base_rs_ms / rs_ms, 3), "speedup_of_medians": med_ratio(brt, rt),
         "fused_per_step_ms": stats(rt), "baseline_per_step_ms": stats(brt),
         "tflops": round(2.0 * M2 * N2 * K2_total / (rs_ms * 1e-3) / 1e12, 1),
+        "raster_group": rs_raster or "default",
+        "rasters_timed": [{"raster_group": a, "ms": round(t, 4)} for a, t in rs_timed],
     }
     fused_rs()
     base_rs()

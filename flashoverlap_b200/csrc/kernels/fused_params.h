@@ -92,6 +92,12 @@ struct StatusWord {
 struct alignas(64) FusedParams {
   CUtensorMap tmA;  // A [M, K] row-major, box 64 x 128, 128-byte swizzle
   CUtensorMap tmB;  // B [N, K] row-major, box 64 x BN,  128-byte swizzle
+  // All-gather -> GEMM: this rank's own rows [a_own_begin, a_own_end) of the
+  // gathered A are read straight from the caller's shard through this map
+  // (row 0 of the map = row a_own_begin), so they are never copied into the
+  // gathered buffer.  a_own_end == a_own_begin: not used.
+  CUtensorMap tmA_own;
+  int a_own_begin, a_own_end;
 
   int M, N, K;
   int TM, TN;        // tile grid (BM = 128)

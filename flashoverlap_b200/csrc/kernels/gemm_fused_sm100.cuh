@@ -675,6 +675,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&p.tmA);
     ptx::prefetch_tensormap(&p.tmB);
+    if (p.a_own_end > p.a_own_begin) ptx::prefetch_tensormap(&p.tmA_own);
   }
   if (warp == 2) {
     if constexpr (CTAS == 2) {
@@ -712,7 +713,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
         tile_coords(p, t, m_blk, n_blk);
         const int a_row = m_blk * TILE_M + static_cast<int>(cta_rank) * BM;
         const int b_row = n_blk * BN + static_cast<int>(cta_rank) * T::B_ROWS;
-        if (p.a_ready != nullptr) {
+        // this CTA's 128 rows of A come from the caller's own shard (never copied) or from the (gathered) A
+        const bool own_rows = a_row >= p.a_own_begin && a_row + BM <= p.a_own_end;
+        const CUtensorMap* map_a = own_rows ? &p.tmA_own : &p.tmA;
+        const int a_row_map = own_rows ? a_row - p.a_own_begin : a_row;
+        if (p.a_ready != nullptr && !own_rows) {
           // Gathered A: wait until every source rank whose rows overlap
           // [a_row, a_row + BM) has delivered them into local memory, then order
           // those generic-proxy writes before the async-proxy (TMA) reads.
@@ -748,13 +753,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
 #pragma unroll
             for (int h = 0; h < T::ATOMS; ++h) {  // one box of 64 K-values per swizzle atom
               if (p.l2_hints) {
-                ptx::tma_load_2d_pair_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                                           kb * BK + h * T::ATOM_K, a_row, pol_a);
+                ptx::tma_load_2d_pair_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, map_a, &full_bar[stage],
+                                           kb * BK + h * T::ATOM_K, a_row_map, pol_a);
                 ptx::tma_load_2d_pair_hint(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
                                            kb * BK + h * T::ATOM_K, b_row, pol_b);
               } else {
-                ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                                      kb * BK + h * T::ATOM_K, a_row);
+                ptx::tma_load_2d_pair(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, map_a, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, a_row_map);
                 ptx::tma_load_2d_pair(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
                                       kb * BK + h * T::ATOM_K, b_row);
               }
@@ -764,13 +769,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fused_sm100_kernel(const __g
 #pragma unroll
             for (int h = 0; h < T::ATOMS; ++h) {
               if (p.l2_hints) {
-                ptx::tma_load_2d_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                                      kb * BK + h * T::ATOM_K, a_row, pol_a);
+                ptx::tma_load_2d_hint(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, map_a, &full_bar[stage],
+                                      kb * BK + h * T::ATOM_K, a_row_map, pol_a);
                 ptx::tma_load_2d_hint(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
                                       kb * BK + h * T::ATOM_K, b_row, pol_b);
               } else {
-                ptx::tma_load_2d(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, &p.tmA, &full_bar[stage],
-                                 kb * BK + h * T::ATOM_K, a_row);
+                ptx::tma_load_2d(smem_a + stage * T::A_BYTES + h * T::A_ATOM_BYTES, map_a, &full_bar[stage],
+                                 kb * BK + h * T::ATOM_K, a_row_map);
                 ptx::tma_load_2d(smem_b + stage * T::B_BYTES + h * T::B_ATOM_BYTES, &p.tmB, &full_bar[stage],
                                  kb * BK + h * T::ATOM_K, b_row);
               }

@@ -103,6 +103,20 @@ cudaError_t launch_fused(const GemmOperands& g, FusedParams& p, cudaStream_t str
     *why = "cuTensorMapEncodeTiled failed";
     return cudaErrorInvalidValue;
   }
+  p.a_own_begin = p.a_own_end = 0;
+  if (g.A_own != nullptr && g.own_rows > 0) {
+    if ((reinterpret_cast<uintptr_t>(g.A_own) & 15u) || g.own_begin < 0 || g.own_begin % 128 != 0 ||
+        g.own_rows % 128 != 0 || g.own_begin + g.own_rows > g.M) {
+      *why = "own rows of A must be 16-byte aligned whole blocks of 128 rows inside the matrix";
+      return cudaErrorInvalidValue;
+    }
+    if (!make_tensor_map(&p.tmA_own, g.A_own, g.own_rows, g.K, 128, g.dtype)) {
+      *why = "cuTensorMapEncodeTiled failed";
+      return cudaErrorInvalidValue;
+    }
+    p.a_own_begin = g.own_begin;
+    p.a_own_end = g.own_begin + g.own_rows;
+  }
   p.M = g.M;
   p.N = g.N;
   p.K = g.K;

@@ -29,6 +29,10 @@ struct GemmOperands {
   DType dtype;
   int algo;
   int sm_count;  // CTAs to launch (<= SMs of the device); 0 = all
+  // Optional: rows [own_begin, own_begin + own_rows) of A are read from A_own
+  // ([own_rows, K] row-major, 16-byte aligned) instead of from A.
+  const void* A_own;
+  int own_begin, own_rows;
 };
 
 // Fills p.tmA / p.tmB / shape fields from `g`, validates shapes, launches.

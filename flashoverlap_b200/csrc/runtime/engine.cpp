@@ -334,7 +334,13 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
     p.owner_stride = rows_local / tc.bm;
   }
   // one GPU: wide groups for L2 reuse; several GPUs: narrow groups so that tile rows complete early
-  if (p.raster_group == 0) p.raster_group = world_ == 1 ? 8 : 2;
+  if (p.raster_group == 0) {
+    // several ranks: a quarter of the tile rows per group, between 2 and 8 (timed on 2 and 4 GPUs: rows
+    // must start completing early, but small groups stream all of B once per group)
+    int rg = (g.M / tc.bm) / 4;
+    rg = rg < 2 ? 2 : (rg > 8 ? 8 : rg);
+    p.raster_group = world_ == 1 ? 8 : rg;
+  }
   p.raster_taper = raster_taper_ ? 1 : 0;
   p.reduce = 1;
   if (row_trace_ != nullptr && g.M <= row_trace_rows_) p.row_trace = row_trace_;
@@ -360,7 +366,8 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
 // first_row: where this rank's own block starts (the GEMM begins there).
 void FusedEngine::gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M,
                                 int first_row, const void* B, void* C, int N, int K, DType dtype, int algo,
-                                const char* op, cudaStream_t stream, size_t mc_slot_offset) {
+                                const char* op, cudaStream_t stream, size_t mc_slot_offset, const void* a_own,
+                                int own_rows) {
   NvtxRange range(op);
   const TileConfig tc = algo_config(algo);
   const int set = static_cast<int>(calls_ & 1ull);
@@ -375,6 +382,9 @@ void FusedEngine::gathered_gemm(const void* const* src_for, const long long* byt
   g.K = K;
   g.dtype = dtype;
   g.algo = algo;
+  g.A_own = a_own;  // this rank's rows are read in place (all-gather), not from the gathered buffer
+  g.own_begin = first_row;
+  g.own_rows = a_own != nullptr ? own_rows : 0;
   p.own_mode = OWN_SINGLE;
   p.ws = world_;
   p.me = rank_;
@@ -437,14 +447,19 @@ void FusedEngine::allgather_gemm(const void* A_shard, const void* B, void* C, in
   const void* src_for[kMaxRanks];
   long long bytes_for[kMaxRanks];
   int src_end[kMaxRanks];
+  // The GEMM reads this rank's own rows straight from the caller's shard (a second TMA descriptor), so
+  // they are not copied into the gathered buffer: nothing is sent to `rank_` itself (the counter is
+  // still bumped).  With the multicast push every rank, this one included, receives the copy anyway.
+  const bool in_place = reinterpret_cast<uintptr_t>(A_shard) % 16 == 0;
+  const bool multicast_push = nvls_available() && nvls_ag_;  // takes the shard's size from the entry of this rank
   for (int r = 0; r < world_; ++r) {
     src_for[r] = A_shard;
-    bytes_for[r] = static_cast<long long>(shard_bytes);
+    bytes_for[r] = (r == rank_ && in_place && !multicast_push) ? 0 : static_cast<long long>(shard_bytes);
     src_end[r] = (r + 1) * rows;
     ag_dst_scratch_[r] = static_cast<char*>(heap_.ptr(r, ws_.stage[set])) + shard_bytes * rank_;
   }
   gathered_gemm(src_for, bytes_for, src_end, M, rank_ * rows, B, C, N, K, dtype, algo, "allgather_gemm", stream,
-                shard_bytes * rank_);
+                shard_bytes * rank_, in_place ? A_shard : nullptr, rows);
 }
 
 int FusedEngine::a2a_padded_rows(const int* mlen, int algo) const {
@@ -512,7 +527,7 @@ void FusedEngine::a2a_gemm(const void* A_send, const void* B, void* C, const int
   if (m_own < tc_own.bm) m_own = tc_own.bm;
   if (m_own > m_pad) m_own = m_pad;
   gathered_gemm(src_for, bytes_for, src_end, m_own, first_row, B, C, N, K, dtype, algo, "a2a_gemm", stream,
-                kNoMulticast);  // every destination gets different rows
+                kNoMulticast, nullptr, 0);  // every destination gets different rows; own rows are copied (ragged blocks)
 }
 
 void FusedEngine::p2p_push(long long bytes, int ctas, cudaStream_t stream) {

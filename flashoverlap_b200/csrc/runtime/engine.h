@@ -139,12 +139,15 @@ class FusedEngine {
   void detach_symmetric();
   bool nvls_available() const { return heap_.valid() && heap_.has_multicast() && world_ > 1; }
   // Which operations take the NVLink SHARP path when it is available.
-  // Default: all-reduce when the group has four or more ranks, reduce-scatter
-  // never.  For an output of S bytes an all-reduce moves S(1+1/n) bytes per
-  // NVLink direction through the switch against 2S(n-1)/n with peer-to-peer
-  // stores: more with two ranks, fewer from four on.  A reduce-scatter moves
-  // S(n-1)/n with peer-to-peer pushes against S pulled through the switch.
-  // Calling set_use_nvls fixes both choices by hand.
+  // Default: none.  For an output of S bytes an all-reduce moves S(1+1/n)
+  // bytes per NVLink direction through the switch against 2S(n-1)/n with
+  // peer-to-peer stores (fewer from four ranks on), but half of the
+  // peer-to-peer traffic, the partial tiles, leaves from the GEMM's epilogue
+  // while the GEMM runs, and the switch can only pull complete rows: measured
+  // with 4 and 8 ranks the peer-to-peer form is the faster one.  A
+  // reduce-scatter moves S(n-1)/n with peer-to-peer pushes against S pulled
+  // through the switch.  set_use_nvls fixes both choices by hand,
+  // set_nvls_auto_min_world makes the all-reduce switch over by group size.
   void set_use_nvls(bool allreduce, bool reducescatter) {
     nvls_ar_ = allreduce ? 1 : 0;
     nvls_rs_ = reducescatter ? 1 : 0;
@@ -206,13 +209,13 @@ class FusedEngine {
   bool l2_hints_ = false;
   bool raster_taper_ = true;
   int nvls_ar_ = -1;  // -1 = by group size, 0 = off, 1 = on
-  int nvls_auto_min_world_ = 4;
+  int nvls_auto_min_world_ = 0;
   int nvls_rs_ = -1;
   void carve_workspace(long long elems);
   static constexpr size_t kNoMulticast = ~size_t(0);
   void gathered_gemm(const void* const* src_for, const long long* bytes_for, const int* src_end, int M, int first_row,
                      const void* B, void* C, int N, int K, DType dtype, int algo, const char* op, cudaStream_t stream,
-                     size_t mc_slot_offset);
+                     size_t mc_slot_offset, const void* a_own, int own_rows);
   // All-gather pushes through the switch (one multimem.st per chunk) deliver every shard at the same time,
   // at the end; the ring of peer-to-peer stores delivers one shard per step in the order the GEMM consumes
   // them, which is what lets the GEMM overlap the transfer: multicast is an option, not the default.

@@ -107,13 +107,19 @@ def make_overlap_impl(group=None, timeout_ms: Optional[int] = None, nvls: Option
 
     ``nvls`` (default: on, unless ``FLASHOVERLAP_NVLS=0``) asks for symmetric
     memory with an NVLink SHARP multicast mapping sized for problems up to
-    ``max_m x max_n``; the fused all-reduce then reduces with ``multimem``
-    instructions (the switch adds the partial tiles and multicasts the
-    results, which moves about a third fewer bytes per NVLink direction than
-    two rounds of peer-to-peer stores).  The ranks agree on the outcome: if the
-    mapping cannot be made on ANY rank, every rank falls back together to the
-    peer-mapped memory the object allocates itself on first use, and the fused
-    operations move data with peer-to-peer stores."""
+    ``max_m x max_n``.  The ranks agree on the outcome: if the mapping cannot be
+    made on ANY rank, every rank falls back together to the peer-mapped memory
+    the object allocates itself on first use.
+
+    With the mapping the fused all-reduce CAN reduce with ``multimem``
+    instructions (the switch adds the partial tiles and multicasts the results:
+    fewer bytes per NVLink direction than two rounds of peer-to-peer stores from
+    four ranks on), but it does so only when asked (``FLASHOVERLAP_NVLS_AR=1`` or
+    ``impl.set_use_nvls(True, False)``): measured on 4 and 8 B200s the
+    peer-to-peer form is faster (0.210 against 0.256 ms with four ranks),
+    because its first half, the partial tiles, travels from the GEMM's epilogue
+    while the GEMM still runs, whereas the switch can only pull rows that are
+    complete.  ``FLASHOVERLAP_NVLS_AR=0`` pins peer-to-peer stores."""
     rank, world = _world(group)
     impl = torch.classes.flashoverlap_class.OverlapImpl()
     impl.nccl_init(rank, world, broadcast_nccl_id(group))
@@ -138,6 +144,9 @@ def make_overlap_impl(group=None, timeout_ms: Optional[int] = None, nvls: Option
             if rank == 0:
                 why = repr(err) if err is not None else "another rank could not map it"
                 print(f"flashoverlap_b200: symmetric memory with multicast unavailable ({why}); using P2P stores")
+    force = os.environ.get("FLASHOVERLAP_NVLS_AR")
+    if force is not None and world > 1:
+        impl.set_use_nvls(force not in ("0", "false", "off"), False)
     env = os.environ.get("FLASHOVERLAP_TIMEOUT_MS")
     if timeout_ms is None and env:
         timeout_ms = int(env)
