@@ -105,11 +105,14 @@ def exhaustive_search(impl, M: int, N: int, K: int, comm_op: str, dtype=torch.fl
     return sol
 
 
-def link_bandwidth_from_curves(world_size: int, multinode: bool = False, path=None) -> Tuple[Optional[float], str]:
-    """Peak of the measured curve of the transport the fused kernel uses
-    (NVLink SHARP all-reduce primitive if it was measured, else peer-to-peer
-    stores), in GB/s, and the name of the file it came from."""
-    for op in ("multimem_allreduce", "p2p_push_bulk", "p2p_push"):
+def link_bandwidth_from_curves(world_size: int, multinode: bool = False, path=None,
+                               nvls: bool = False) -> Tuple[Optional[float], str]:
+    """Peak of the measured curve of the transport the fused kernel uses, in
+    GB/s, and the name of the file it came from: peer-to-peer stores, or with
+    ``nvls`` (the engine's all-reduce is set to NVLink SHARP) the ``multimem``
+    all-reduce primitive if that curve was measured."""
+    order = ("multimem_allreduce", "p2p_push", "p2p_push_bulk") if nvls else ("p2p_push", "p2p_push_bulk")
+    for op in order:
         try:
             c = cfg.load_bandwidth(op, world_size, multinode, path)
         except FileNotFoundError:

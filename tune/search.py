@@ -40,7 +40,8 @@ def run(args, rank, world):
     multinode = args.multinode or int(os.environ.get("GROUP_WORLD_SIZE", "1")) > 1
     if args.predictive_search or M * N > search.PREDICTIVE_THRESHOLD:
         curve = cfg.load_bandwidth(args.comm_op, world, multinode, args.path)
-        link, kind = search.link_bandwidth_from_curves(world, multinode, args.path)
+        nvls = args.comm_op == "all_reduce" and world > 1 and impl.allreduce_uses_nvls()
+        link, kind = search.link_bandwidth_from_curves(world, multinode, args.path, nvls=nvls)
         if link is None and world > 1 and impl.transport() == "p2p":
             raise SystemExit("no curve of the library's own transport found: run tune/bandwidth.py --comm_op p2p_push "
                              "(and multimem_allreduce where NVLink SHARP is available) first")
