@@ -269,7 +269,7 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     else:
         check["a2a_max_err"] = 0.0
 
-    # ---- verdict -------------------------------------------------------------------------------
+    # ---- outcome -------------------------------------------------------------------------------
     impl.check_status()
     tol = {"ar_max_err": 1e-2, "ar_vs_nccl_baseline_max_err": 1e-2, "two_stream_max_err": 1e-2, "rs_max_err": 5e-2,
            "rs_vs_nccl_baseline_max_err": 5e-2, "ag_max_err": 5e-2, "a2a_max_err": 1e-2}
