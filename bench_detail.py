@@ -132,19 +132,22 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
     O2 = torch.empty_like(D2)
     F2 = torch.empty_like(D2)
 
-    # raster group (tile rows walked together) of this shape, searched like the tuner's stage 2: timed candidates
-    rs_raster, rs_timed = 0, []
+    # tile configuration and raster group (tile rows walked together) of this shape, searched like the tuner's
+    # stage 2: timed candidates
+    # (with this much K per rank the 64-deep pipeline stage of Algo 3 can beat the 128-deep one of Algo 8)
+    rs_algo, rs_raster, rs_timed = algo, 0, []
     if world > 1:
-        def run_raster(rg):
-            impl.set_raster_group(rg)
-            impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, algo, False)
+        def run_cand(c):
+            impl.set_raster_group(c[1])
+            impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, c[0], False)
 
-        rs_raster, rs_timed = pick_algo_by_timing(run_raster, [2, 4, 8], warmup=1, reps=3)
+        cands = [(a, rg) for a in dict.fromkeys([algo, 3]) for rg in (4, 8)] + [(algo, 2)]
+        (rs_algo, rs_raster), rs_timed = pick_algo_by_timing(run_cand, cands, warmup=1, reps=3)
         impl.set_raster_group(0)
 
     def fused_rs():
         impl.set_raster_group(rs_raster)
-        impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, algo, False)
+        impl.gemm_reducescatter_fused(A2, B2, F2, W2, eps, rs_algo, False)
         impl.set_raster_group(0)
 
     def base_rs():
@@ -159,8 +162,8 @@ def run_detail(impl, layer, x, steps, warmup, algo, mx, stats):
         "speedup_vs_nccl_baseline": round(base_rs_ms / rs_ms, 3), "speedup_of_medians": med_ratio(brt, rt),
         "fused_per_step_ms": stats(rt), "baseline_per_step_ms": stats(brt),
         "tflops": round(2.0 * M2 * N2 * K2_total / (rs_ms * 1e-3) / 1e12, 1),
-        "raster_group": rs_raster or "default",
-        "rasters_timed": [{"raster_group": a, "ms": round(t, 4)} for a, t in rs_timed],
+        "algo": rs_algo, "raster_group": rs_raster or "default",
+        "candidates_timed": [{"algo": c[0], "raster_group": c[1], "ms": round(t, 4)} for c, t in rs_timed],
     }
     fused_rs()
     base_rs()
