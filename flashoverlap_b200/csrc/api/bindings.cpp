@@ -10,6 +10,7 @@
 #include <torch/custom_class.h>
 #include <torch/library.h>
 
+#include "../kernels/fused_params.h"
 #include "../kernels/rmsnorm.h"
 #include "baseline_impl.h"
 #include "checks.h"
@@ -78,6 +79,33 @@ static void rmsnorm_op(at::Tensor X, at::Tensor O, at::Tensor RW, double eps) {
                                  static_cast<int>(X.size(1)), static_cast<float>(eps), dt,
                                  at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(e == cudaSuccess, "rmsnorm launch failed: ", cudaGetErrorString(e));
+}
+
+// The order in which the persistent kernel walks the tile grid, computed on
+// the host by the function the kernel itself uses: entry i is
+// tile_row * TN + tile_column of the i-th tile of the walk.  For tests and for
+// tools that reason about completion order without a GPU.
+static std::vector<int64_t> tile_walk_op(int64_t TM, int64_t TN, int64_t raster_group, bool taper, int64_t owner_stride,
+                                         int64_t ws, int64_t me, int64_t rot) {
+  TORCH_CHECK(TM > 0 && TN > 0 && TM * TN <= (1 << 24), "tile grid out of range");
+  TORCH_CHECK(ws >= 1 && me >= 0 && me < ws && rot >= 0 && rot < TM, "rank or rotation out of range");
+  TORCH_CHECK(owner_stride == 0 || owner_stride * ws == TM, "owner_stride must be TM / ws (or 0)");
+  FusedParams p{};
+  p.TM = static_cast<int>(TM);
+  p.TN = static_cast<int>(TN);
+  p.raster_group = static_cast<int>(raster_group < 1 ? 1 : (raster_group > TM ? TM : raster_group));
+  p.raster_taper = taper ? 1 : 0;
+  p.owner_stride = static_cast<int>(owner_stride);
+  p.ws = static_cast<int>(ws);
+  p.me = static_cast<int>(me);
+  p.rot = static_cast<int>(rot);
+  std::vector<int64_t> out(static_cast<size_t>(TM * TN));
+  for (int t = 0; t < p.TM * p.TN; ++t) {
+    int m_blk = 0, n_blk = 0;
+    tile_coords(p, t, m_blk, n_blk);
+    out[static_cast<size_t>(t)] = static_cast<int64_t>(m_blk) * TN + n_blk;
+  }
+  return out;
 }
 
 }  // namespace fo
@@ -165,4 +193,5 @@ TORCH_LIBRARY(flashoverlap_op, m) {
   m.def("reorder_rmsnorm", &fo::reorder_rmsnorm_op);
   m.def("reorder_rmsnorm_eps", &fo::reorder_rmsnorm_eps);
   m.def("rmsnorm", &fo::rmsnorm_op);
+  m.def("tile_walk", &fo::tile_walk_op);
 }

@@ -15,6 +15,12 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#if defined(__CUDACC__)
+#define FO_HOST_DEVICE __host__ __device__
+#else
+#define FO_HOST_DEVICE
+#endif
+
 namespace fo {
 
 constexpr int kMaxRanks = 8;
@@ -189,5 +195,53 @@ struct alignas(64) FusedParams {
   StatusWord* status_mirror;  // mapped host memory, may be null
   unsigned long long timeout_ns;
 };
+
+// Tile order: tile rows are walked in groups of `raster_group`; inside a group
+// the walk is column-major so that one B panel serves the whole group from L2
+// and tile rows still complete early and in order.  With `raster_taper` the
+// last groups shrink (G, ..., G, G/2, G/4, ..., 1, 1): the rows of a group can
+// only be reduced once the whole group is computed, so the size of the LAST
+// group is what remains to be communicated after the last tile.
+FO_HOST_DEVICE inline void tile_coords(const FusedParams& p, int t, int& m_blk, int& n_blk) {
+  const int G = p.raster_group;
+  int first = 0;      // first tile row of the group that holds tile t
+  int rows_here = G;  // tile rows in that group
+  int r = t;          // index of the tile inside the group
+  if (!p.raster_taper) {
+    const int per_group = G * p.TN;
+    const int g = t / per_group;
+    r = t - g * per_group;
+    first = g * G;
+    rows_here = (p.TM - first) < G ? (p.TM - first) : G;
+  } else {
+    // full groups while more than G tile rows remain, then halves
+    int remaining = p.TM;
+    int size = G;
+    while (true) {
+      if (remaining <= size) size = remaining > 1 ? (remaining + 1) / 2 : 1;
+      const int tiles_here = size * p.TN;
+      if (r < tiles_here || remaining == size) break;
+      r -= tiles_here;
+      first += size;
+      remaining -= size;
+    }
+    rows_here = size;
+  }
+  int mb = first + r % rows_here;
+  n_blk = r / rows_here;
+  if (p.owner_stride > 0) {
+    // Contiguous row ownership: position mb of the walk is tile row
+    // (mb % ws) of ... every owner in turn, so that any stretch of the walk
+    // sends to all owners alike and every owner's rows complete progressively
+    // (walking owner by owner would complete an owner's rows only when the
+    // LAST rank reaches its block, i.e. at the very end).  Each rank starts the
+    // cycle at a different owner.
+    const int o = (mb + p.me) % p.ws;
+    mb = o * p.owner_stride + mb / p.ws;
+  }
+  m_blk = mb + p.rot;
+  if (m_blk >= p.TM) m_blk -= p.TM;
+}
+
 
 }  // namespace fo
