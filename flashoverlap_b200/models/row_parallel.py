@@ -99,11 +99,16 @@ class FusedRowParallelLinear(nn.Module):
     :func:`flashoverlap_b200.parallel.make_overlap_impl`); ``norm_weight`` turns
     the fused RMSNorm on.  With ``comm_op="all_reduce"`` the returned tensor
     aliases the implementation's symmetric result buffer and stays valid until
-    the second next fused call on the same ``impl``."""
+    the second next fused call on the same ``impl``.
+
+    ``algo`` and ``raster_group`` are what the tuner searches for a shape
+    (``tune/search.py`` stores them as ``Algo`` and ``raster_group`` in the
+    stage-2 JSON; :meth:`from_config` reads them); ``raster_group=0`` leaves the
+    library's default."""
 
     def __init__(self, impl, in_features: int, out_features: int, comm_op: str = "all_reduce",
                  norm: bool = False, eps: float = 1e-5, algo: int = 0, interleave: bool = False,
-                 dtype=torch.float16, device=None):
+                 dtype=torch.float16, device=None, raster_group: int = 0):
         super().__init__()
         assert comm_op in ("all_reduce", "reduce_scatter"), f"unknown comm_op {comm_op!r}"
         dev = _device(device)
@@ -111,6 +116,7 @@ class FusedRowParallelLinear(nn.Module):
         self.comm_op = comm_op
         self.eps = eps
         self.algo = algo
+        self.raster_group = int(raster_group)
         self.interleave = interleave
         self.world_size = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
         self.weight = nn.Parameter(torch.randn(out_features, in_features, dtype=dtype, device=dev) /
@@ -118,14 +124,29 @@ class FusedRowParallelLinear(nn.Module):
         self.norm_weight: Optional[nn.Parameter] = (
             nn.Parameter(torch.ones(out_features, dtype=dtype, device=dev)) if norm else None)
 
+    @classmethod
+    def from_config(cls, impl, config: dict, in_features: int, out_features: int, **kwargs):
+        """A layer that runs the tile configuration and raster group a search
+        found (``config``: the stage-2 dictionary of
+        :func:`flashoverlap_b200.utils.config.load_config`)."""
+        kwargs.setdefault("comm_op", config.get("comm_op", "all_reduce"))
+        return cls(impl, in_features, out_features, algo=int(config["Algo"]),
+                   raster_group=int(config.get("raster_group", 0)), **kwargs)
+
     @torch.no_grad()
     def forward(self, x):
-        if self.comm_op == "all_reduce":
-            return self.impl.gemm_allreduce_fused(x, self.weight, self.norm_weight, self.eps, self.algo)
-        out = torch.empty((x.size(0) // self.world_size, self.weight.size(0)), dtype=x.dtype, device=x.device)
-        self.impl.gemm_reducescatter_fused(x, self.weight, out, self.norm_weight, self.eps, self.algo,
-                                           self.interleave)
-        return out
+        if self.raster_group:
+            self.impl.set_raster_group(self.raster_group)  # a host-side setting of the next launches
+        try:
+            if self.comm_op == "all_reduce":
+                return self.impl.gemm_allreduce_fused(x, self.weight, self.norm_weight, self.eps, self.algo)
+            out = torch.empty((x.size(0) // self.world_size, self.weight.size(0)), dtype=x.dtype, device=x.device)
+            self.impl.gemm_reducescatter_fused(x, self.weight, out, self.norm_weight, self.eps, self.algo,
+                                               self.interleave)
+            return out
+        finally:
+            if self.raster_group:
+                self.impl.set_raster_group(0)
 
 
 class HierarchicalRowParallelLinear(nn.Module):

@@ -118,3 +118,35 @@ def test_clock_sampler_with_a_fake_nvml(monkeypatch):
     assert out["samples"] >= 1 and out["sm_mhz"] == 1400 and out["sm_max_mhz"] == 1965
     assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 950.0
     assert not any(name.startswith("nvmlDeviceSet") for name in dir(fake))
+
+
+def test_fused_layer_runs_the_searched_configuration():
+    """FusedRowParallelLinear.from_config hands the tuner's Algo and raster group to the kernel call."""
+    import torch
+
+    from flashoverlap_b200.models import FusedRowParallelLinear
+
+    class FakeImpl:
+        def __init__(self):
+            self.calls = []
+
+        def set_raster_group(self, g):
+            self.calls.append(("raster", g))
+
+        def gemm_allreduce_fused(self, x, w, gamma, eps, algo):
+            self.calls.append(("ar", algo, gamma is not None))
+            return torch.zeros(x.size(0), w.size(0))
+
+        def gemm_reducescatter_fused(self, x, w, out, gamma, eps, algo, interleave):
+            self.calls.append(("rs", algo, interleave))
+
+    impl = FakeImpl()
+    cfg_ar = {"Algo": 8, "raster_group": 4, "comm_op": "all_reduce"}
+    layer = FusedRowParallelLinear.from_config(impl, cfg_ar, 64, 128, norm=True, device="cpu")
+    y = layer(torch.zeros(256, 64, dtype=torch.float16))
+    assert y.shape == (256, 128)
+    assert impl.calls == [("raster", 4), ("ar", 8, True), ("raster", 0)]   # set for the call, then back to the default
+    impl.calls.clear()
+    layer = FusedRowParallelLinear.from_config(impl, {"Algo": 3, "comm_op": "reduce_scatter"}, 64, 128, device="cpu")
+    out = layer(torch.zeros(256, 64, dtype=torch.float16))
+    assert out.shape == (256, 128) and impl.calls == [("rs", 3, False)]    # no raster group in the file: untouched
