@@ -243,6 +243,14 @@ void* FusedEngine::gemm_allreduce(const GemmOperands& g_in, void* out_user, cons
   ensure_workspace(g.M, g.N);
   const int set = static_cast<int>(calls_ & 1ull);
   check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  if (world_ == 1 && norm.gamma == nullptr && sig == nullptr && out_layout == nullptr) {
+    // One rank and no RMSNorm: nothing to sum or scale, the GEMM writes the result itself.  The buffer
+    // sets still alternate (and the other set's counters are cleared above) like after any fused call.
+    void* result = out_user != nullptr ? out_user : heap_.local(ws_.result[set]);
+    gemm(g, result, nullptr, nullptr, stream);
+    ++calls_;
+    return result;
+  }
 
   FusedParams p;
   base_params(p, sig);
@@ -311,6 +319,11 @@ void FusedEngine::gemm_reducescatter(const GemmOperands& g_in, void* D, bool int
   ensure_workspace(g.M, g.N);
   const int set = static_cast<int>(calls_ & 1ull);
   check(cudaMemsetAsync(flag_ptr(rank_, set ^ 1), 0, kFlagWords * 4, stream), "cudaMemsetAsync(counters)");
+  if (world_ == 1 && norm.gamma == nullptr && sig == nullptr && out_layout == nullptr) {
+    gemm(g, D, nullptr, nullptr, stream);  // one rank, no RMSNorm: the GEMM writes the rows where they belong
+    ++calls_;
+    return;
+  }
 
   FusedParams p;
   base_params(p, sig);
