@@ -134,7 +134,7 @@ struct alignas(64) FusedParams {
   const uint32_t* a_ready;  // per source-rank counter; null = A is ready at launch
   uint32_t a_ready_target;
   int a_src_end[kMaxRanks]; // source r contributed the rows [a_src_end[r-1], a_src_end[r]) of the gathered A
-  // All-gather push (done by warp 2 of every CTA while the GEMM starts on this
+  // All-gather push (done by the communication warps of every CTA while the GEMM starts on this
   // rank's own shard): this rank's shard goes to every rank's gathered A.
   // (all-gather: the same shard to everybody; all-to-all dispatch: a different
   // block of rows, possibly empty, to every rank).
